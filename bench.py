@@ -1,0 +1,319 @@
+#!/usr/bin/env python
+"""Benchmark of the latent decode-attention op on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+One "step" = one pass of the op (split-KV stage 1 + merge, U_v applied) over the whole
+batch of one decoder layer.  Rank 0 prints ONE JSON line.
+
+* N = 1: workload c2 (LLaVA-1.5-13B shape: B16, 40 heads, head_dim 128, rank 64/64,
+  context 8192), inputs resident in HBM and larger than L2.
+* N > 1 (launched under torchrun, one rank per GPU): every rank owns a head shard of
+  that same shape (weak scaling: 40 local heads per GPU) and the step ends with the
+  path's one exchange, an NCCL all-gather of the [B, H_local, 128] outputs.
+* `value` = algorithmic latent+scale bytes of all ranks / max-over-ranks device time.
+* `e2e` = the same step through the public Python op with the per-step inputs (q and
+  the batch metadata) copied from pinned host memory and the result copied back to the
+  host inside the timed region; the latent KV cache is resident device state, as in the
+  reference (its caches are CUDA tensors, efficiency/layer_utils.py:57-58).
+* `roofline` is for the dominant kernel (stage 1), timed alone with CUDA events.
+* `cpu_baseline` / `--impl reference`: the reference's own CPU-runnable torch path
+  (restated in oracle/) on the host cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "latent decode-attn µs/layer & achieved HBM GB/s (1/2/4/8 B200), 7B/13B shapes"
+DEFAULT_WORKLOAD = "c2_13b_b16_s8192"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms during the timed region."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_reference_run(spec, steps, warmup, sample_batch=2):
+    """The reference's CPU-runnable path (oracle restatement of
+    efficiency/test_functional_layer.py:146-163 with the kernel's RoPE) on all host
+    threads, on `sample_batch` sequences of the workload per step."""
+    from oracle import latent_decode_oracle as orc
+    from wsvd_b200 import inputs
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    lens = inputs.seq_lens_for(spec)[:sample_batch]
+    case = inputs.make_case(len(lens), spec.heads, spec.head_dim, spec.rank_k, spec.rank_v, lens, spec.max_len,
+                            spec.seed, device="cpu", poison=False)
+    nbytes = inputs.algorithmic_bytes(lens, spec.heads, spec.rank_k, spec.rank_v)
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        orc.latent_decode_oracle(*case.oracle_args(), wv=case.wv)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+    t = sum(times) / len(times)
+    return {
+        "value": nbytes / t / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+        "sample": f"{len(lens)} of {spec.batch} sequences of {spec.name} per step "
+                  f"({nbytes / 1e6:.1f} MB of latents+scales), torch {torch.__version__} fp32",
+        "ms_per_step_sample": t * 1e3,
+        "us_per_layer_extrapolated": t * 1e6 * (spec.batch / len(lens)),
+    }
+
+
+def run_reference(args, spec):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 10))
+    warm = max(1, min(args.warmup, 2))
+    cb = cpu_reference_run(spec, steps, warm)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": warm, "ms_per_step": cb["ms_per_step_sample"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "i8 latents, f32 math", "data": "synthetic",
+        "config": {"workload": spec.name, "batch": spec.batch, "heads": spec.heads, "head_dim": spec.head_dim,
+                   "rank_k": spec.rank_k, "rank_v": spec.rank_v, "context": spec.max_len,
+                   "l2": "CPU run; sample larger than the host caches"},
+        "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "us_per_layer_extrapolated": cb["us_per_layer_extrapolated"],
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--kernel", default="auto", choices=["auto", "generic", "tc"])
+    ap.add_argument("--split-len", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    from wsvd_b200 import inputs
+
+    spec = inputs.WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, spec)
+        return
+
+    import ctypes
+
+    from wsvd_b200 import _lib, ops
+    from wsvd_b200.kernel.flash_decoding import token_decode_attention_flash_int8_latent_per_head_decoding_rope as op
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the op has no CPU path")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch N>1 under torch.distributed.run")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    args.warmup = max(args.warmup, 3)
+
+    # ---- workload: this rank's head shard, generated on the device ----
+    shard_spec = inputs.WorkloadSpec(**{**spec.__dict__, "seed": spec.seed + 7919 * rank})
+    case = inputs.make_workload(shard_spec, device=dev)
+    st = case.infer_state
+    B, H, D = case.q.shape
+    lens = case.seq_lens
+    bytes_rank = inputs.algorithmic_bytes(lens, H, spec.rank_k, spec.rank_v)
+    bytes_total = bytes_rank * world
+    out = torch.empty(B, H, D, dtype=torch.float16, device=dev)
+    gathered = torch.empty(world, B, H, D, dtype=torch.float16, device=dev) if world > 1 else None
+    p, _keep = ops.build_params(case.q, st.b_seq_len, st.b_req_idx, st.req_manager.req_to_token_indexs,
+                                st.max_len_in_batch, case.latent_k, case.k_scale, case.latent_v, case.v_scale,
+                                case.wk, None, wv=case.wv, out=out, split_len=args.split_len, kernel=args.kernel)
+    split_len, n_splits = ops.plan(p)
+    ws = torch.empty((ops.workspace_bytes(p) + 3) // 4, dtype=torch.float32, device=dev)
+    stream = torch.cuda.current_stream()
+    lib = _lib.lib()
+
+    def step():
+        _lib.check(lib.wsvd_latent_decode(ctypes.byref(p), ctypes.c_void_p(ws.data_ptr()), ws.numel() * 4,
+                                          ctypes.c_void_p(stream.cuda_stream)), "wsvd_latent_decode")
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, out)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, k):
+        """k calls bracketed by barrier+synchronize; device time by CUDA events, max over ranks."""
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(k):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item()
+
+    for _ in range(args.warmup):
+        step()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms_total = timed(step, args.steps)
+    ms_step = ms_total / args.steps
+
+    # ---- dominant kernel alone (stage 1), for the roofline ----
+    mid_o = ws[: B * H * n_splits * spec.rank_v]
+    lse = ws[B * H * n_splits * spec.rank_v:]
+    p1, _k1 = ops.build_params(case.q, st.b_seq_len, st.b_req_idx, st.req_manager.req_to_token_indexs,
+                               st.max_len_in_batch, case.latent_k, case.k_scale, case.latent_v, case.v_scale,
+                               case.wk, None, split_len=split_len, kernel=args.kernel)
+
+    def stage1():
+        _lib.check(lib.wsvd_latent_decode_stage1(ctypes.byref(p1), ctypes.c_void_p(mid_o.data_ptr()),
+                                                 ctypes.c_void_p(lse.data_ptr()), n_splits,
+                                                 ctypes.c_void_p(stream.cuda_stream)), "stage1")
+
+    for _ in range(3):
+        stage1()
+    ms_stage1 = timed(stage1, args.steps) / args.steps
+
+    # ---- end to end through the public op, host buffers in, host result out ----
+    q_host = case.q.cpu().pin_memory()
+    len_host = st.b_seq_len.cpu().pin_memory()
+    req_host = st.b_req_idx.cpu().pin_memory()
+    out_host = torch.empty(B, H, D, dtype=torch.float16).pin_memory()
+    q_dev, len_dev, req_dev = torch.empty_like(case.q), torch.empty_like(st.b_seq_len), torch.empty_like(st.b_req_idx)
+    from wsvd_b200.infer_state import InferState
+    st2 = InferState(B, st.max_len_in_batch, lens, device=dev, req_to_token=st.req_manager.req_to_token_indexs)
+    st2.b_seq_len, st2.b_req_idx = len_dev, req_dev
+
+    def e2e_step():
+        q_dev.copy_(q_host, non_blocking=True)
+        len_dev.copy_(len_host, non_blocking=True)
+        req_dev.copy_(req_host, non_blocking=True)
+        o = op(q_dev, st2, H, D, case.latent_k, case.k_scale, case.latent_v, case.v_scale, case.wk, None,
+               wv=case.wv, out=out, workspace=ws, split_len=args.split_len, kernel=args.kernel)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, o)
+        out_host.copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the caller consumes the host result every step
+
+    for _ in range(3):
+        e2e_step()
+    ms_e2e = timed(e2e_step, args.steps) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+    h2d = q_host.numel() * 2 + len_host.numel() * 4 + req_host.numel() * 4
+    d2h = out_host.numel() * 2
+
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        achieved = bytes_rank / (ms_stage1 * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": bytes_total / (ms_step * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "us_per_layer": ms_step * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "i8 latents, f16 tensor-core operands, f32 accumulate/softmax", "data": "synthetic",
+            "config": {
+                "workload": spec.name, "batch": spec.batch, "heads_per_gpu": H, "head_dim": D,
+                "rank_k": spec.rank_k, "rank_v": spec.rank_v, "context": spec.max_len, "split_len": split_len,
+                "n_splits": n_splits, "kernel": args.kernel, "parallelism": f"heads x{world}",
+                "collective": "nccl all_gather of [B,H_local,128] f16" if world > 1 else "none",
+                "l2": f"inputs {bytes_rank / 1e6:.0f} MB per GPU, larger than the 126 MB L2",
+            },
+            "roofline": {
+                "bound": "hbm", "kernel": "latent decode stage 1", "achieved": achieved, "peak": peak,
+                "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
+                "us_per_launch": ms_stage1 * 1e3, "algorithmic_bytes_per_launch": bytes_rank, "traffic": None,
+            },
+            "e2e": {"value": bytes_total / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "us_per_layer": ms_e2e * 1e3,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": args.steps * 2,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            cb = cpu_reference_run(spec, steps=3, warmup=1)
+            line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
+            line["cpu_baseline"]["us_per_layer_extrapolated"] = cb["us_per_layer_extrapolated"]
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,136 @@
+/*
+ * wsvd_b200 — C ABI of the B200 (sm_100a) latent flash-decoding library.
+ *
+ * Every entry point takes plain pointers and sizes.  The library never allocates or
+ * frees device memory and never synchronises the device: all work is enqueued on the
+ * stream the caller passes (a cudaStream_t cast to void*; NULL = the legacy default
+ * stream).  All functions return a WsvdStatus (0 = success) and never throw or abort.
+ *
+ * Tensor conventions follow the reference (WSVD, efficiency/kernel/):
+ *   q            [B, Hq, D]          f16, innermost stride 1
+ *   latent_k/v   [T, Hkv, Rk|Rv]     int8 (with f16 scales [T, Hkv]) or f16
+ *   wk           [Rk, Hkv*D]         f16, or int8 with a per-column f16 scale [Hkv*D]
+ *   req_to_token [n_req, max_len]    int32 page table: logical position -> token slot
+ *   b_req_idx, b_seq_len [B]         int32
+ * Strides are in ELEMENTS of the tensor's own dtype.  The innermost dimension of every
+ * tensor must be contiguous.  A head-major cache [B, H, S, R] is expressed with
+ * stride_t = R, stride_h = S*R and a page table req_to_token[b][s] = b*H*S + s.
+ */
+#ifndef WSVD_B200_H_
+#define WSVD_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define WSVD_ABI_VERSION 1
+
+typedef enum WsvdStatus {
+  WSVD_OK = 0,
+  WSVD_ERR_NULL_POINTER = 1,     /* a required pointer is NULL */
+  WSVD_ERR_BAD_SHAPE = 2,        /* head_dim/rank/head counts outside the supported set */
+  WSVD_ERR_BAD_DTYPE = 3,        /* unknown dtype code, or scales missing for int8 */
+  WSVD_ERR_BAD_STRIDE = 4,       /* stride/alignment precondition violated */
+  WSVD_ERR_WORKSPACE_TOO_SMALL = 5,
+  WSVD_ERR_CUDA = 6,             /* a CUDA runtime call failed; see wsvd_last_cuda_error() */
+  WSVD_ERR_UNSUPPORTED = 7,      /* valid request that this build has no kernel for */
+  WSVD_ERR_TOO_LARGE = 8         /* size beyond a documented fixed limit */
+} WsvdStatus;
+
+typedef enum WsvdDtype { WSVD_I8 = 0, WSVD_F16 = 1 } WsvdDtype;
+typedef enum WsvdRopeLayout { WSVD_ROPE_HALF = 0, WSVD_ROPE_INTERLEAVED = 1 } WsvdRopeLayout;
+
+/* Which stage-1 kernel to run.  AUTO picks the tcgen05 kernel when the shape allows. */
+typedef enum WsvdKernel { WSVD_KERNEL_AUTO = 0, WSVD_KERNEL_GENERIC = 1, WSVD_KERNEL_TC = 2 } WsvdKernel;
+
+/*
+ * Arguments of the latent decode-attention op.  Mirrors the tensors that
+ * token_decode_attention_flash_int8_latent_per_head_decoding_rope and its f16 sibling
+ * pass to their kernels (efficiency/kernel/flash_decoding.py:3-55, :57-95;
+ * flash_int8_latent_per_head_decoding_rope_stage1.py:33-56,250-280).
+ */
+typedef struct WsvdLatentDecodeParams {
+  const void* q;            int64_t q_stride_b, q_stride_h;
+  const void* latent_k;     int64_t k_stride_t, k_stride_h;
+  const void* k_scale;      int64_t ks_stride_t, ks_stride_h;   /* NULL for f16 latents */
+  const void* latent_v;     int64_t v_stride_t, v_stride_h;
+  const void* v_scale;      int64_t vs_stride_t, vs_stride_h;   /* NULL for f16 latents */
+  const void* wk;           int64_t wk_stride_r;                /* [Rk, Hkv*D], column stride 1 */
+  const void* wk_scale;                                         /* f16 [Hkv*D], NULL when wk is f16 */
+  const void* wv;           int64_t wv_stride_r;                /* optional f16 [Rv, Hkv*D]: out = O_lat . wv */
+  const int32_t* req_to_token; int64_t rtt_stride;              /* row stride; column stride 1 */
+  const int32_t* b_req_idx;
+  const int32_t* b_seq_len;
+  const int32_t* pos_offset;  /* optional [B]: RoPE position of token s is pos_offset[b] + s */
+  void* out;                int64_t out_stride_b, out_stride_h; /* f16 [B,Hq,Rv], or [B,Hq,D] when wv != NULL */
+  int32_t batch, n_q_heads, n_kv_heads, head_dim, rank_k, rank_v;
+  int32_t max_len;          /* >= every b_seq_len[b]; sizes the grid and the workspace */
+  int32_t latent_dtype;     /* WsvdDtype of latent_k/latent_v */
+  int32_t wk_dtype;         /* WsvdDtype of wk */
+  int32_t rope_layout;      /* WsvdRopeLayout; the reference kernels use HALF */
+  int32_t split_len;        /* tokens per split-KV partial; 0 = library default */
+  int32_t kernel;           /* WsvdKernel */
+  float theta;              /* RoPE base, 10000 in the reference (stage1.py:269) */
+  float sm_scale;           /* 0 = 1/sqrt(head_dim) (stage1.py:244) */
+} WsvdLatentDecodeParams;
+
+/* Version of this header the library was built from. */
+int wsvd_abi_version(void);
+
+/* Static text for a status code. */
+const char* wsvd_status_string(int status);
+
+/* cudaError_t (as int) of the last failed CUDA call made by this library on the
+ * calling thread, 0 if none. */
+int wsvd_last_cuda_error(void);
+
+/*
+ * Split plan shared by the workspace query and the launch: tokens per split and
+ * number of split slots per (b, h).  Replaces the BLOCK_SEQ constant that the reference
+ * hard-codes on the host (flash_decoding.py:18,31-36) while its kernel autotunes it.
+ */
+int wsvd_latent_decode_plan(const WsvdLatentDecodeParams* p, int32_t* split_len, int32_t* n_splits);
+
+/* Bytes of scratch the op needs: partials [B,Hq,n_splits,Rv] f32 + lse [B,Hq,n_splits] f32
+ * (the mid_o / mid_o_logexpsum tensors of flash_decoding.py:31-36). */
+size_t wsvd_latent_decode_workspace_bytes(const WsvdLatentDecodeParams* p);
+
+/*
+ * The whole op: split-KV stage 1 then the merge, on `stream`.
+ * Replaces token_decode_attention_flash_int8_latent_per_head_decoding_rope
+ * (flash_decoding.py:3-55) and token_decode_attention_flash_latent_per_head_decoding_rope
+ * (flash_decoding.py:57-95), selected by p->latent_dtype.
+ */
+int wsvd_latent_decode(const WsvdLatentDecodeParams* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Stage 1 alone, writing normalised partials mid_o [B,Hq,n_splits,Rv] f32 (contiguous)
+ * and lse [B,Hq,n_splits] f32 for splits of p->split_len tokens (must be > 0 here).
+ * Replaces flash_int8_latent_per_head_decode_rope_stage1
+ * (flash_int8_latent_per_head_decoding_rope_stage1.py:221-281) and
+ * flash_latent_per_head_decode_rope_stage1 (flash_latent_per_head_decoding_rope_stage1.py:169-213).
+ * p->out and p->wv are ignored.
+ */
+int wsvd_latent_decode_stage1(const WsvdLatentDecodeParams* p, float* mid_o, float* lse, int32_t n_splits, void* stream);
+
+/*
+ * Stage 2 alone: merge the first ceil(len_b/split_len) partials of every (b, h) by
+ * their log-sum-exp weights; a sequence of length 0 yields zeros.
+ * Replaces flash_decode_stage2 (flash_latent_per_head_decoding_stage2.py:52-69 and
+ * flash_decoding_stage2.py:48-64).  `width` is Rv (or D for the dense op).
+ * When wv != NULL (f16 [width, n_kv_heads*head_dim], row stride wv_stride_r) the merged
+ * row is multiplied by the head's slice of wv and `out` is [B,Hq,head_dim].
+ */
+int wsvd_decode_stage2(const float* mid_o, const float* lse, const int32_t* b_seq_len,
+                       void* out, int64_t out_stride_b, int64_t out_stride_h,
+                       int32_t batch, int32_t n_q_heads, int32_t n_splits, int32_t width, int32_t split_len,
+                       const void* wv, int64_t wv_stride_r, int32_t n_kv_heads, int32_t head_dim,
+                       void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif  /* WSVD_B200_H_ */

@@ -1,0 +1,176 @@
+// extern "C" entry points: validation, split plan, launches.  No allocation, no
+// synchronisation; everything is enqueued on the caller's stream.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+thread_local int g_last_cuda_error = 0;
+
+int cuda_fail(cudaError_t e) {
+  g_last_cuda_error = (int)e;
+  return WSVD_ERR_CUDA;
+}
+
+bool is_pow2_dim(int d) { return d == 16 || d == 32 || d == 64 || d == 128; }
+
+// Preconditions of the reference wrappers (stage1.py:231-243) plus the ones its kernels
+// assume silently (contiguous innermost dims, positive sizes).
+int validate(const WsvdLatentDecodeParams* p, bool need_out) {
+  if (!p) return WSVD_ERR_NULL_POINTER;
+  if (!p->q || !p->latent_k || !p->latent_v || !p->wk || !p->req_to_token || !p->b_req_idx || !p->b_seq_len)
+    return WSVD_ERR_NULL_POINTER;
+  if (need_out && !p->out) return WSVD_ERR_NULL_POINTER;
+  if (p->latent_dtype != WSVD_I8 && p->latent_dtype != WSVD_F16) return WSVD_ERR_BAD_DTYPE;
+  if (p->wk_dtype != WSVD_I8 && p->wk_dtype != WSVD_F16) return WSVD_ERR_BAD_DTYPE;
+  if (p->latent_dtype == WSVD_I8 && (!p->k_scale || !p->v_scale)) return WSVD_ERR_BAD_DTYPE;
+  if (p->wk_dtype == WSVD_I8 && !p->wk_scale) return WSVD_ERR_BAD_DTYPE;
+  if (p->rope_layout != WSVD_ROPE_HALF && p->rope_layout != WSVD_ROPE_INTERLEAVED) return WSVD_ERR_BAD_DTYPE;
+  if (p->batch < 0 || p->max_len < 0) return WSVD_ERR_BAD_SHAPE;
+  if (!is_pow2_dim(p->head_dim)) return WSVD_ERR_BAD_SHAPE;
+  if (p->n_q_heads <= 0 || p->n_kv_heads <= 0 || p->n_q_heads % p->n_kv_heads != 0) return WSVD_ERR_BAD_SHAPE;
+  if (p->rank_k <= 0 || p->rank_k > 128 || p->rank_v <= 0 || p->rank_v > 128) return WSVD_ERR_BAD_SHAPE;
+  if (p->batch > 65535 || p->n_q_heads > 65535) return WSVD_ERR_TOO_LARGE;
+  if (p->split_len < 0) return WSVD_ERR_BAD_SHAPE;
+  if (p->kernel < WSVD_KERNEL_AUTO || p->kernel > WSVD_KERNEL_TC) return WSVD_ERR_BAD_DTYPE;
+  if (!(p->theta > 0.f)) return WSVD_ERR_BAD_SHAPE;
+  return WSVD_OK;
+}
+
+void plan(const WsvdLatentDecodeParams* p, int* split_len, int* n_splits) {
+  int sl = p->split_len;
+  if (sl <= 0) {
+    // enough (b, h, split) items to fill 148 SMs a few times over, but never splits
+    // shorter than 256 tokens (the reference's BLOCK_SEQ, flash_decoding.py:18)
+    const long items = (long)p->batch * p->n_q_heads;
+    const long target = 148L * 8;
+    long want = items > 0 ? (target + items - 1) / items : 1;
+    if (want < 1) want = 1;
+    long len = (p->max_len + want - 1) / want;
+    len = ((len + 127) / 128) * 128;
+    if (len < 256) len = 256;
+    if (len > 4096) len = 4096;
+    sl = (int)len;
+  }
+  *split_len = sl;
+  int ns = (p->max_len + sl - 1) / sl;
+  *n_splits = ns < 1 ? 1 : ns;
+}
+
+void fill_args(const WsvdLatentDecodeParams* p, float* mid_o, float* lse, int split_len, int n_splits,
+               wsvd::KArgs* a) {
+  a->p = *p;
+  const int h2 = p->head_dim / 2;
+  for (int i = 0; i < wsvd::kMaxHalfDim; ++i)
+    a->inv_freq[i] = i < h2 ? (float)(1.0 / pow((double)p->theta, (2.0 * i) / (double)p->head_dim)) : 0.f;
+  a->mid_o = mid_o;
+  a->lse = lse;
+  a->split_len = split_len;
+  a->n_splits = n_splits;
+  a->sm_scale = p->sm_scale != 0.f ? p->sm_scale : (float)(1.0 / sqrt((double)p->head_dim));
+}
+
+int run_stage1(const wsvd::KArgs& a, cudaStream_t stream) {
+  if (a.p.batch == 0) return WSVD_OK;
+  if (a.p.kernel == WSVD_KERNEL_TC) return WSVD_ERR_UNSUPPORTED;
+  cudaError_t e = wsvd::launch_stage1_generic(a, stream);
+  return e == cudaSuccess ? WSVD_OK : cuda_fail(e);
+}
+
+}  // namespace
+
+extern "C" {
+
+int wsvd_abi_version(void) { return WSVD_ABI_VERSION; }
+
+const char* wsvd_status_string(int status) {
+  switch (status) {
+    case WSVD_OK: return "ok";
+    case WSVD_ERR_NULL_POINTER: return "a required pointer is NULL";
+    case WSVD_ERR_BAD_SHAPE: return "unsupported head_dim / rank / head count / length";
+    case WSVD_ERR_BAD_DTYPE: return "unknown dtype or layout code, or int8 data without its scales";
+    case WSVD_ERR_BAD_STRIDE: return "stride or alignment precondition violated";
+    case WSVD_ERR_WORKSPACE_TOO_SMALL: return "workspace smaller than wsvd_latent_decode_workspace_bytes()";
+    case WSVD_ERR_CUDA: return "a CUDA runtime call failed (see wsvd_last_cuda_error)";
+    case WSVD_ERR_UNSUPPORTED: return "no kernel in this build for the requested combination";
+    case WSVD_ERR_TOO_LARGE: return "size beyond a fixed limit of this entry point";
+    default: return "unknown status";
+  }
+}
+
+int wsvd_last_cuda_error(void) { return g_last_cuda_error; }
+
+int wsvd_latent_decode_plan(const WsvdLatentDecodeParams* p, int32_t* split_len, int32_t* n_splits) {
+  if (!split_len || !n_splits) return WSVD_ERR_NULL_POINTER;
+  if (!p) return WSVD_ERR_NULL_POINTER;
+  if (p->max_len < 0 || p->split_len < 0 || p->batch < 0 || p->n_q_heads <= 0) return WSVD_ERR_BAD_SHAPE;
+  int sl, ns;
+  plan(p, &sl, &ns);
+  *split_len = sl;
+  *n_splits = ns;
+  return WSVD_OK;
+}
+
+size_t wsvd_latent_decode_workspace_bytes(const WsvdLatentDecodeParams* p) {
+  if (!p || p->max_len < 0 || p->split_len < 0 || p->batch < 0 || p->n_q_heads <= 0 || p->rank_v <= 0) return 0;
+  int sl, ns;
+  plan(p, &sl, &ns);
+  const size_t slots = (size_t)p->batch * p->n_q_heads * ns;
+  return slots * ((size_t)p->rank_v + 1) * sizeof(float);
+}
+
+int wsvd_latent_decode(const WsvdLatentDecodeParams* p, void* workspace, size_t workspace_bytes, void* stream) {
+  int st = validate(p, true);
+  if (st != WSVD_OK) return st;
+  if (p->batch == 0) return WSVD_OK;
+  const size_t need = wsvd_latent_decode_workspace_bytes(p);
+  if (!workspace) return WSVD_ERR_NULL_POINTER;
+  if (workspace_bytes < need) return WSVD_ERR_WORKSPACE_TOO_SMALL;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 15) != 0) return WSVD_ERR_BAD_STRIDE;
+  int sl, ns;
+  plan(p, &sl, &ns);
+  const size_t slots = (size_t)p->batch * p->n_q_heads * ns;
+  float* mid_o = reinterpret_cast<float*>(workspace);
+  float* lse = mid_o + slots * p->rank_v;
+  wsvd::KArgs a;
+  fill_args(p, mid_o, lse, sl, ns, &a);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  st = run_stage1(a, s);
+  if (st != WSVD_OK) return st;
+  cudaError_t e = wsvd::launch_stage2(mid_o, lse, p->b_seq_len, p->out, p->out_stride_b, p->out_stride_h, p->batch,
+                                      p->n_q_heads, ns, p->rank_v, sl, p->wv, p->wv_stride_r, p->n_kv_heads,
+                                      p->head_dim, s);
+  return e == cudaSuccess ? WSVD_OK : cuda_fail(e);
+}
+
+int wsvd_latent_decode_stage1(const WsvdLatentDecodeParams* p, float* mid_o, float* lse, int32_t n_splits,
+                              void* stream) {
+  int st = validate(p, false);
+  if (st != WSVD_OK) return st;
+  if (!mid_o || !lse) return WSVD_ERR_NULL_POINTER;
+  if (p->split_len <= 0) return WSVD_ERR_BAD_SHAPE;
+  if ((long)n_splits * p->split_len < p->max_len) return WSVD_ERR_WORKSPACE_TOO_SMALL;
+  wsvd::KArgs a;
+  fill_args(p, mid_o, lse, p->split_len, n_splits, &a);
+  return run_stage1(a, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int wsvd_decode_stage2(const float* mid_o, const float* lse, const int32_t* b_seq_len, void* out,
+                       int64_t out_stride_b, int64_t out_stride_h, int32_t batch, int32_t n_q_heads,
+                       int32_t n_splits, int32_t width, int32_t split_len, const void* wv, int64_t wv_stride_r,
+                       int32_t n_kv_heads, int32_t head_dim, void* stream) {
+  if (!mid_o || !lse || !b_seq_len || !out) return WSVD_ERR_NULL_POINTER;
+  if (batch < 0 || n_q_heads <= 0 || n_splits <= 0 || split_len <= 0) return WSVD_ERR_BAD_SHAPE;
+  if (width <= 0 || width > 128) return WSVD_ERR_BAD_SHAPE;
+  if (batch > 65535) return WSVD_ERR_TOO_LARGE;
+  if (wv && (n_kv_heads <= 0 || n_q_heads % n_kv_heads != 0 || head_dim <= 0 || head_dim > 1024))
+    return WSVD_ERR_BAD_SHAPE;
+  if (batch == 0) return WSVD_OK;
+  cudaError_t e = wsvd::launch_stage2(mid_o, lse, b_seq_len, out, out_stride_b, out_stride_h, batch, n_q_heads,
+                                      n_splits, width, split_len, wv, wv_stride_r, wv ? n_kv_heads : 1, head_dim,
+                                      reinterpret_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? WSVD_OK : cuda_fail(e);
+}
+
+}  // extern "C"

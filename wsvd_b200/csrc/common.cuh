@@ -1,0 +1,46 @@
+// Shared device-side definitions for the latent flash-decoding kernels.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "wsvd_b200.h"
+
+namespace wsvd {
+
+constexpr int kMaxHalfDim = 64;  // head_dim <= 128
+
+// Kernel argument block, passed by value (__grid_constant__).
+struct KArgs {
+  WsvdLatentDecodeParams p;
+  float inv_freq[kMaxHalfDim];  // theta^(-2i/D), rounded once from double on the host
+  float* mid_o;                 // [B, Hq, n_splits, Rv] normalised partials
+  float* lse;                   // [B, Hq, n_splits]     max + log(sum)
+  int32_t split_len;
+  int32_t n_splits;
+  float sm_scale;
+};
+
+__device__ __forceinline__ float to_float(int8_t v) { return static_cast<float>(v); }
+__device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Launchers implemented in the kernel translation units.
+cudaError_t launch_stage1_generic(const KArgs& a, cudaStream_t stream);
+cudaError_t launch_stage2(const float* mid_o, const float* lse, const int32_t* b_seq_len, void* out,
+                          int64_t out_stride_b, int64_t out_stride_h, int batch, int n_q_heads, int n_splits,
+                          int width, int split_len, const void* wv, int64_t wv_stride_r, int n_kv_heads,
+                          int head_dim, cudaStream_t stream);
+
+}  // namespace wsvd

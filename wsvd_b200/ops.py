@@ -1,0 +1,210 @@
+"""Tensor -> C-ABI marshalling for the latent decode-attention op.
+
+The functions here take torch CUDA tensors, check the preconditions the reference
+wrappers assert (efficiency/kernel/flash_int8_latent_per_head_decoding_rope_stage1.py:
+231-243) and call libwsvd_b200.so on the current CUDA stream.  No CPU path exists.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Callable, Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import LatentDecodeParams, check
+
+I8, F16 = 0, 1
+ROPE = {"half": 0, "interleaved": 1}
+KERNEL = {"auto": 0, "generic": 1, "tc": 2}
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _need(cond: bool, msg: str, exc=ValueError):
+    if not cond:
+        raise exc(msg)
+
+
+def _cuda_tensor(name, t, dtypes, ndim):
+    _need(isinstance(t, torch.Tensor), f"{name} must be a torch.Tensor", TypeError)
+    _need(t.is_cuda, f"{name} must be a CUDA tensor (no CPU path exists)")
+    _need(t.dtype in dtypes, f"{name} has dtype {t.dtype}, expected one of {dtypes}", TypeError)
+    _need(t.dim() == ndim, f"{name} must have {ndim} dims, got {tuple(t.shape)}")
+    _need(t.numel() == 0 or t.stride(-1) == 1, f"{name}: innermost dimension must be contiguous")
+
+
+def build_params(
+    q, b_seq_len, b_req_idx, req_to_token, max_len, latent_k, k_scale, latent_v, v_scale, wk, wk_scale=None,
+    wv=None, out=None, pos_offset=None, theta=10000.0, sm_scale=0.0, rope_layout="half", split_len=0,
+    kernel="auto",
+) -> Tuple[LatentDecodeParams, list]:
+    """Validate tensors and fill a WsvdLatentDecodeParams.  Returns the struct and the
+    list of tensors it points into (keep them alive until the launch is enqueued)."""
+    _cuda_tensor("q", q, (torch.float16,), 3)
+    B, Hq, D = q.shape
+    _cuda_tensor("cache_latent_k", latent_k, (torch.int8, torch.float16), 3)
+    _cuda_tensor("cache_latent_v", latent_v, (torch.int8, torch.float16), 3)
+    _need(latent_k.dtype == latent_v.dtype, "latent K and V must share a dtype", TypeError)
+    is_i8 = latent_k.dtype == torch.int8
+    Hkv, Rk = latent_k.shape[1], latent_k.shape[2]
+    Rv = latent_v.shape[2]
+    _need(latent_v.shape[1] == Hkv, "latent K and V disagree on the number of KV heads")
+    _need(Hq % Hkv == 0, f"q heads ({Hq}) must be a multiple of KV heads ({Hkv})")
+    _need(D in (16, 32, 64, 128), f"head_dim {D} not in {{16, 32, 64, 128}}")
+    _need(1 <= Rk <= 128 and 1 <= Rv <= 128, "per-head rank must be in [1, 128]")
+    _cuda_tensor("wk", wk, (torch.int8, torch.float16), 2)
+    _need(wk.shape[1] == D * Hkv, f"wk.shape[1] ({wk.shape[1]}) != head_dim * kv_heads ({D * Hkv})")
+    _need(wk.shape[0] == Rk, f"wk.shape[0] ({wk.shape[0]}) != rank_k ({Rk})")
+    if is_i8:
+        _need(k_scale is not None and v_scale is not None, "int8 latents need k_scale and v_scale", TypeError)
+        _cuda_tensor("cache_latent_k_scale", k_scale, (torch.float16,), 2)
+        _cuda_tensor("cache_latent_v_scale", v_scale, (torch.float16,), 2)
+        _need(k_scale.shape[0] == latent_k.shape[0] and k_scale.shape[1] == Hkv, "k_scale must be [T, Hkv]")
+        _need(v_scale.shape[0] == latent_v.shape[0] and v_scale.shape[1] == Hkv, "v_scale must be [T, Hkv]")
+    else:
+        _need(k_scale is None and v_scale is None, "f16 latents take no scales", TypeError)
+    if wk.dtype == torch.int8:
+        _need(wk_scale is not None, "int8 wk needs wk_scale", TypeError)
+        _need(wk_scale.is_cuda and wk_scale.dtype == torch.float16, "wk_scale must be a CUDA f16 tensor", TypeError)
+        _need(wk_scale.numel() == D * Hkv and wk_scale.is_contiguous(),
+              f"wk_scale must hold head_dim * kv_heads = {D * Hkv} contiguous values")
+    else:
+        _need(wk_scale is None, "f16 wk takes no wk_scale", TypeError)
+    if wv is not None:
+        _cuda_tensor("wv", wv, (torch.float16,), 2)
+        _need(tuple(wv.shape) == (Rv, D * Hkv), f"wv must be [rank_v, head_dim*kv_heads] = {(Rv, D * Hkv)}")
+    for name, t in (("b_seq_len", b_seq_len), ("b_req_idx", b_req_idx)):
+        _cuda_tensor(name, t, (torch.int32,), 1)
+        _need(t.shape[0] == B, f"{name} must have batch ({B}) entries")
+    _cuda_tensor("req_to_token_indexs", req_to_token, (torch.int32,), 2)
+    _need(0 <= max_len <= req_to_token.shape[1], "max_len_in_batch exceeds the page-table width")
+    if pos_offset is not None:
+        _cuda_tensor("pos_offset", pos_offset, (torch.int32,), 1)
+        _need(pos_offset.shape[0] == B, "pos_offset must have batch entries")
+    out_w = D if wv is not None else Rv
+    if out is not None:
+        _cuda_tensor("out", out, (torch.float16,), 3)
+        _need(tuple(out.shape) == (B, Hq, out_w), f"out must be {(B, Hq, out_w)}, got {tuple(out.shape)}")
+    _need(rope_layout in ROPE, f"rope_layout must be one of {list(ROPE)}")
+    _need(kernel in KERNEL, f"kernel must be one of {list(KERNEL)}")
+
+    p = LatentDecodeParams()
+    p.q, p.q_stride_b, p.q_stride_h = q.data_ptr(), q.stride(0), q.stride(1)
+    p.latent_k, p.k_stride_t, p.k_stride_h = latent_k.data_ptr(), latent_k.stride(0), latent_k.stride(1)
+    p.latent_v, p.v_stride_t, p.v_stride_h = latent_v.data_ptr(), latent_v.stride(0), latent_v.stride(1)
+    if is_i8:
+        p.k_scale, p.ks_stride_t, p.ks_stride_h = k_scale.data_ptr(), k_scale.stride(0), k_scale.stride(1)
+        p.v_scale, p.vs_stride_t, p.vs_stride_h = v_scale.data_ptr(), v_scale.stride(0), v_scale.stride(1)
+    p.wk, p.wk_stride_r = wk.data_ptr(), wk.stride(0)
+    p.wk_scale = None if wk_scale is None else wk_scale.data_ptr()
+    if wv is not None:
+        p.wv, p.wv_stride_r = wv.data_ptr(), wv.stride(0)
+    p.req_to_token, p.rtt_stride = req_to_token.data_ptr(), req_to_token.stride(0)
+    p.b_req_idx, p.b_seq_len = b_req_idx.data_ptr(), b_seq_len.data_ptr()
+    p.pos_offset = None if pos_offset is None else pos_offset.data_ptr()
+    if out is not None:
+        p.out, p.out_stride_b, p.out_stride_h = out.data_ptr(), out.stride(0), out.stride(1)
+    p.batch, p.n_q_heads, p.n_kv_heads, p.head_dim, p.rank_k, p.rank_v = B, Hq, Hkv, D, Rk, Rv
+    p.max_len = int(max_len)
+    p.latent_dtype = I8 if is_i8 else F16
+    p.wk_dtype = I8 if wk.dtype == torch.int8 else F16
+    p.rope_layout = ROPE[rope_layout]
+    p.split_len = int(split_len)
+    p.kernel = KERNEL[kernel]
+    p.theta, p.sm_scale = float(theta), float(sm_scale)
+    keep = [q, latent_k, latent_v, k_scale, v_scale, wk, wk_scale, wv, req_to_token, b_req_idx, b_seq_len,
+            pos_offset, out]
+    return p, keep
+
+
+def plan(p: LatentDecodeParams) -> Tuple[int, int]:
+    sl, ns = ctypes.c_int32(), ctypes.c_int32()
+    check(_lib.lib().wsvd_latent_decode_plan(ctypes.byref(p), ctypes.byref(sl), ctypes.byref(ns)), "plan")
+    return sl.value, ns.value
+
+
+def workspace_bytes(p: LatentDecodeParams) -> int:
+    return int(_lib.lib().wsvd_latent_decode_workspace_bytes(ctypes.byref(p)))
+
+
+def _stream(stream) -> ctypes.c_void_p:
+    s = torch.cuda.current_stream() if stream is None else stream
+    return ctypes.c_void_p(s.cuda_stream)
+
+
+@torch.no_grad()
+def latent_decode(
+    q, infer_state, latent_k, k_scale, latent_v, v_scale, wk, wk_scale=None, *, wv=None, out=None,
+    workspace: Optional[torch.Tensor] = None, alloc_tensor_func: Callable = torch.empty, pos_offset=None,
+    theta=10000.0, rope_layout="half", split_len=0, kernel="auto", stream=None,
+) -> torch.Tensor:
+    """Fused latent decode attention.  Returns O_lat [B,Hq,Rv] (f16), or O [B,Hq,D] when
+    `wv` ([Rv, Hkv*D] f16) is given.  `workspace` is an optional CUDA byte/float buffer of
+    at least workspace_bytes(); when absent it is taken from `alloc_tensor_func`."""
+    B = int(infer_state.batch_size)
+    q3 = q.view(B, q.shape[-2], q.shape[-1]) if q.dim() != 3 else q
+    p, keep = build_params(
+        q3, infer_state.b_seq_len, infer_state.b_req_idx, infer_state.req_manager.req_to_token_indexs,
+        int(infer_state.max_len_in_batch), latent_k, k_scale, latent_v, v_scale, wk, wk_scale, wv=wv, out=out,
+        pos_offset=pos_offset, theta=theta, rope_layout=rope_layout, split_len=split_len, kernel=kernel)
+    if out is None:
+        out_w = p.head_dim if wv is not None else p.rank_v
+        out = alloc_tensor_func((B, p.n_q_heads, out_w), dtype=q.dtype, device=q.device)
+        p.out, p.out_stride_b, p.out_stride_h = out.data_ptr(), out.stride(0), out.stride(1)
+    need = workspace_bytes(p)
+    if workspace is None:
+        workspace = alloc_tensor_func(((need + 3) // 4,), dtype=torch.float32, device=q.device)
+    else:
+        _need(workspace.is_cuda and workspace.is_contiguous(), "workspace must be a contiguous CUDA tensor")
+    have = workspace.numel() * workspace.element_size()
+    with torch.cuda.device(q.device):
+        check(_lib.lib().wsvd_latent_decode(ctypes.byref(p), _ptr(workspace), have, _stream(stream)),
+              "wsvd_latent_decode")
+    return out
+
+
+@torch.no_grad()
+def latent_decode_stage1(q, latent_k, k_scale, latent_v, v_scale, wk, wk_scale, req_to_token, b_req_idx, b_seq_len,
+                         max_len, mid_out, mid_out_lse, block_seq, *, theta=10000.0, rope_layout="half",
+                         kernel="auto", stream=None):
+    """Split-KV stage 1 into caller-owned partial buffers mid_out [B,Hq,n_splits,Rv] f32
+    and mid_out_lse [B,Hq,n_splits] f32."""
+    p, keep = build_params(q, b_seq_len, b_req_idx, req_to_token, int(max_len), latent_k, k_scale, latent_v, v_scale,
+                           wk, wk_scale, theta=theta, rope_layout=rope_layout, split_len=int(block_seq),
+                           kernel=kernel)
+    _need(mid_out.is_cuda and mid_out.dtype == torch.float32 and mid_out.is_contiguous(), "mid_out: contiguous CUDA f32")
+    _need(mid_out_lse.is_cuda and mid_out_lse.dtype == torch.float32 and mid_out_lse.is_contiguous(),
+          "mid_out_logsumexp: contiguous CUDA f32")
+    B, Hq, ns, Rv = mid_out.shape
+    _need((B, Hq, Rv) == (p.batch, p.n_q_heads, p.rank_v), "mid_out must be [B, Hq, n_splits, rank_v]")
+    _need(tuple(mid_out_lse.shape) == (B, Hq, ns), "mid_out_logsumexp must be [B, Hq, n_splits]")
+    with torch.cuda.device(q.device):
+        check(_lib.lib().wsvd_latent_decode_stage1(ctypes.byref(p), _ptr(mid_out), _ptr(mid_out_lse), ns,
+                                                   _stream(stream)), "wsvd_latent_decode_stage1")
+
+
+@torch.no_grad()
+def decode_stage2(mid_out, mid_out_lse, b_seq_len, out, block_seq, *, wv=None, n_kv_heads=None, stream=None):
+    """Split-KV stage 2: merge partials by log-sum-exp weights into `out` (f16)."""
+    for name, t in (("mid_out", mid_out), ("mid_out_logexpsum", mid_out_lse)):
+        _need(t.is_cuda and t.dtype == torch.float32 and t.is_contiguous(), f"{name}: contiguous CUDA f32")
+    B, Hq, ns, W = mid_out.shape
+    _need(tuple(mid_out_lse.shape) == (B, Hq, ns), "mid_out_logexpsum must be [B, Hq, n_splits]")
+    _cuda_tensor("B_Seqlen", b_seq_len, (torch.int32,), 1)
+    _cuda_tensor("O", out, (torch.float16,), 3)
+    head_dim, hkv, wv_stride = 0, 1, 0
+    if wv is not None:
+        _cuda_tensor("wv", wv, (torch.float16,), 2)
+        hkv = int(n_kv_heads or Hq)
+        head_dim = wv.shape[1] // hkv
+        wv_stride = wv.stride(0)
+        _need(tuple(out.shape) == (B, Hq, head_dim), "out must be [B, Hq, head_dim] when wv is given")
+    else:
+        _need(tuple(out.shape) == (B, Hq, W), "out must be [B, Hq, width]")
+    with torch.cuda.device(out.device):
+        check(_lib.lib().wsvd_decode_stage2(
+            _ptr(mid_out), _ptr(mid_out_lse), _ptr(b_seq_len), _ptr(out), out.stride(0), out.stride(1),
+            B, Hq, ns, W, int(block_seq), _ptr(wv), wv_stride, hkv, head_dim, _stream(stream)), "wsvd_decode_stage2")
