@@ -75,6 +75,8 @@ typedef struct WsvdLatentDecodeParams {
   int32_t kernel;           /* WsvdKernel */
   float theta;              /* RoPE base, 10000 in the reference (stage1.py:269) */
   float sm_scale;           /* 0 = 1/sqrt(head_dim) (stage1.py:244) */
+  const void* rope_table;   /* optional: table made by wsvd_rope_table_init for the same theta/head_dim */
+  int32_t rope_table_rows;  /* positions it covers (>= max_len rounded up to 128) */
 } WsvdLatentDecodeParams;
 
 /* Version of this header the library was built from. */
@@ -86,6 +88,25 @@ const char* wsvd_status_string(int status);
 /* cudaError_t (as int) of the last failed CUDA call made by this library on the
  * calling thread, 0 if none. */
 int wsvd_last_cuda_error(void);
+
+/*
+ * cos/sin position table used by the tensor-core kernel (the reference recomputes
+ * cos/sin per tile with fast-math intrinsics, stage1.py:8-14,157-159).  It depends only on
+ * theta, head_dim and the number of positions, so a caller can build it once and pass it in
+ * WsvdLatentDecodeParams.rope_table; without it wsvd_latent_decode rebuilds it in the
+ * workspace on every call.  `positions` is rounded up to a multiple of 128 by both calls.
+ */
+size_t wsvd_rope_table_bytes(int32_t positions, int32_t head_dim);
+int wsvd_rope_table_init(void* table, size_t table_bytes, int32_t positions, int32_t head_dim, float theta,
+                         void* stream);
+
+/*
+ * Device-side status of the tensor-core kernel: 0, or the code of the first bounded wait
+ * that timed out (1 producer, 2 MMA issuer, 3 epilogue).  SYNCHRONISES the device; meant
+ * for tests and diagnostics.  wsvd_kernel_status_reset clears it.
+ */
+int wsvd_kernel_status(uint32_t* status);
+int wsvd_kernel_status_reset(void);
 
 /*
  * Split plan shared by the workspace query and the launch: tokens per split and

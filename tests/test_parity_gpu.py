@@ -3,7 +3,7 @@ import pytest
 import torch
 
 from tests.helpers import assert_close, oracle_for
-from wsvd_b200 import inputs
+from wsvd_b200 import inputs, ops
 from wsvd_b200.kernel.flash_decoding import (
     token_decode_attention_flash_int8_latent_per_head_decoding_rope as op_i8,
     token_decode_attention_flash_latent_per_head_decoding_rope as op_f16,
@@ -20,6 +20,8 @@ def run_i8(case, kernel, wv=False, **kw):
     out = op_i8(c.q, s, c.q.shape[1], c.q.shape[2], c.latent_k, c.k_scale, c.latent_v, c.v_scale, c.wk, None,
                 wv=c.wv if wv else None, kernel=kernel, **kw)
     torch.cuda.synchronize()
+    if kernel != "generic":
+        assert ops.kernel_status() == 0, "a bounded wait in the tensor-core kernel timed out"
     return out
 
 
@@ -86,9 +88,9 @@ def test_long_positions_against_fp64(kernel):
 
 
 @pytest.mark.parametrize("kernel", ["generic"])
-@pytest.mark.parametrize("d", [16, 32, 64])
-def test_small_head_dims_generic(kernel, d):
-    case = inputs.make_case(2, 2, d, 16, 32, [100, 37], 100, seed=d)
+@pytest.mark.parametrize("d,rk,rv", [(16, 16, 16), (32, 16, 32), (64, 32, 48)])
+def test_small_head_dims_generic(kernel, d, rk, rv):
+    case = inputs.make_case(2, 2, d, rk, rv, [100, 37], 100, seed=d)
     assert_close(run_i8(case, kernel), oracle_for(case), f"D={d}")
 
 

@@ -85,6 +85,7 @@ class LatentDecodeParams(ctypes.Structure):
         ("latent_dtype", ctypes.c_int32), ("wk_dtype", ctypes.c_int32), ("rope_layout", ctypes.c_int32),
         ("split_len", ctypes.c_int32), ("kernel", ctypes.c_int32),
         ("theta", ctypes.c_float), ("sm_scale", ctypes.c_float),
+        ("rope_table", ctypes.c_void_p), ("rope_table_rows", ctypes.c_int32),
     ]
 
 
@@ -94,6 +95,11 @@ SYMBOLS = {
     "wsvd_abi_version": (ctypes.c_int, []),
     "wsvd_status_string": (ctypes.c_char_p, [ctypes.c_int]),
     "wsvd_last_cuda_error": (ctypes.c_int, []),
+    "wsvd_rope_table_bytes": (ctypes.c_size_t, [ctypes.c_int32, ctypes.c_int32]),
+    "wsvd_rope_table_init": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int32, ctypes.c_int32,
+                                            ctypes.c_float, ctypes.c_void_p]),
+    "wsvd_kernel_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_uint32)]),
+    "wsvd_kernel_status_reset": (ctypes.c_int, []),
     "wsvd_latent_decode_plan": (ctypes.c_int, [_P, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]),
     "wsvd_latent_decode_workspace_bytes": (ctypes.c_size_t, [_P]),
     "wsvd_latent_decode": (ctypes.c_int, [_P, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),

@@ -38,9 +38,42 @@ int validate(const WsvdLatentDecodeParams* p, bool need_out) {
   return WSVD_OK;
 }
 
+bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; }
+
+// The tensor-core kernel covers the decode shapes of the 7B/13B models; everything else
+// runs on the generic kernel.
+bool tc_eligible(const WsvdLatentDecodeParams* p) {
+  if (p->kernel == WSVD_KERNEL_GENERIC) return false;
+  if (p->head_dim != 128 || p->rank_k != 64) return false;
+  if (p->rank_v % 16 != 0 || p->rank_v > 64) return false;
+  if (p->latent_dtype != WSVD_I8 || p->pos_offset != nullptr) return false;
+  if (p->split_len % 128 != 0) return false;
+  if (!aligned16(p->latent_k) || !aligned16(p->latent_v)) return false;
+  if (p->k_stride_t % 16 || p->k_stride_h % 16 || p->v_stride_t % 16 || p->v_stride_h % 16) return false;
+  if (p->rope_table && (!aligned16(p->rope_table) || p->rope_table_rows < ((p->max_len + 127) / 128) * 128))
+    return false;
+  return true;
+}
+
+int table_rows_for(int max_len) {
+  int rows = ((max_len + 127) / 128) * 128;
+  return rows < 128 ? 128 : rows;
+}
+
 void plan(const WsvdLatentDecodeParams* p, int* split_len, int* n_splits) {
   int sl = p->split_len;
-  if (sl <= 0) {
+  if (sl <= 0 && tc_eligible(p)) {
+    // one CTA per (split, group of 4 heads, sequence): aim at ~6 CTAs per SM
+    const long items = (long)p->batch * ((p->n_q_heads + 3) / 4);
+    const long target = 148L * 6;
+    long want = items > 0 ? (target + items - 1) / items : 1;
+    if (want < 1) want = 1;
+    long len = (p->max_len + want - 1) / want;
+    len = ((len + 127) / 128) * 128;
+    if (len < 128) len = 128;
+    if (len > 8192) len = 8192;
+    sl = (int)len;
+  } else if (sl <= 0) {
     // enough (b, h, split) items to fill 148 SMs a few times over, but never splits
     // shorter than 256 tokens (the reference's BLOCK_SEQ, flash_decoding.py:18)
     const long items = (long)p->batch * p->n_q_heads;
@@ -71,11 +104,31 @@ void fill_args(const WsvdLatentDecodeParams* p, float* mid_o, float* lse, int sp
   a->sm_scale = p->sm_scale != 0.f ? p->sm_scale : (float)(1.0 / sqrt((double)p->head_dim));
 }
 
-int run_stage1(const wsvd::KArgs& a, cudaStream_t stream) {
+// `scratch_table`: where to build the position table when the caller gave none (may be null).
+int run_stage1(const wsvd::KArgs& a, void* scratch_table, cudaStream_t stream) {
   if (a.p.batch == 0) return WSVD_OK;
-  if (a.p.kernel == WSVD_KERNEL_TC) return WSVD_ERR_UNSUPPORTED;
-  cudaError_t e = wsvd::launch_stage1_generic(a, stream);
+  const bool tc = tc_eligible(&a.p) && a.split_len % 128 == 0 && (a.p.rope_table || scratch_table);
+  if (!tc) {
+    if (a.p.kernel == WSVD_KERNEL_TC) return WSVD_ERR_UNSUPPORTED;
+    cudaError_t e = wsvd::launch_stage1_generic(a, stream);
+    return e == cudaSuccess ? WSVD_OK : cuda_fail(e);
+  }
+  const void* table = a.p.rope_table;
+  int rows = a.p.rope_table_rows;
+  if (!table) {
+    rows = table_rows_for(a.p.max_len);
+    cudaError_t e = wsvd::launch_rope_table(scratch_table, rows, a, stream);
+    if (e != cudaSuccess) return cuda_fail(e);
+    table = scratch_table;
+  }
+  cudaError_t e = wsvd::launch_stage1_tc(a, table, rows, stream);
   return e == cudaSuccess ? WSVD_OK : cuda_fail(e);
+}
+
+size_t partial_bytes(const WsvdLatentDecodeParams* p, int ns) {
+  const size_t slots = (size_t)p->batch * p->n_q_heads * ns;
+  const size_t b = slots * ((size_t)p->rank_v + 1) * sizeof(float);
+  return (b + 255) & ~(size_t)255;
 }
 
 }  // namespace
@@ -116,8 +169,44 @@ size_t wsvd_latent_decode_workspace_bytes(const WsvdLatentDecodeParams* p) {
   if (!p || p->max_len < 0 || p->split_len < 0 || p->batch < 0 || p->n_q_heads <= 0 || p->rank_v <= 0) return 0;
   int sl, ns;
   plan(p, &sl, &ns);
-  const size_t slots = (size_t)p->batch * p->n_q_heads * ns;
-  return slots * ((size_t)p->rank_v + 1) * sizeof(float);
+  size_t bytes = partial_bytes(p, ns);
+  if (tc_eligible(p) && !p->rope_table) bytes += wsvd::rope_table_bytes(table_rows_for(p->max_len));
+  return bytes;
+}
+
+size_t wsvd_rope_table_bytes(int32_t positions, int32_t head_dim) {
+  if (positions < 0 || head_dim != 128) return 0;
+  return wsvd::rope_table_bytes(table_rows_for(positions));
+}
+
+int wsvd_rope_table_init(void* table, size_t table_bytes, int32_t positions, int32_t head_dim, float theta,
+                         void* stream) {
+  if (!table) return WSVD_ERR_NULL_POINTER;
+  if (head_dim != 128) return WSVD_ERR_UNSUPPORTED;
+  if (positions < 0 || !(theta > 0.f)) return WSVD_ERR_BAD_SHAPE;
+  if (!aligned16(table)) return WSVD_ERR_BAD_STRIDE;
+  const int rows = table_rows_for(positions);
+  if (table_bytes < wsvd::rope_table_bytes(rows)) return WSVD_ERR_WORKSPACE_TOO_SMALL;
+  WsvdLatentDecodeParams p = {};
+  p.head_dim = head_dim;
+  p.theta = theta;
+  wsvd::KArgs a;
+  fill_args(&p, nullptr, nullptr, 128, 1, &a);
+  cudaError_t e = wsvd::launch_rope_table(table, rows, a, reinterpret_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? WSVD_OK : cuda_fail(e);
+}
+
+int wsvd_kernel_status(uint32_t* status) {
+  if (!status) return WSVD_ERR_NULL_POINTER;
+  unsigned int v = 0;
+  cudaError_t e = wsvd::read_tc_status(&v);
+  *status = v;
+  return e == cudaSuccess ? WSVD_OK : cuda_fail(e);
+}
+
+int wsvd_kernel_status_reset(void) {
+  cudaError_t e = wsvd::reset_tc_status();
+  return e == cudaSuccess ? WSVD_OK : cuda_fail(e);
 }
 
 int wsvd_latent_decode(const WsvdLatentDecodeParams* p, void* workspace, size_t workspace_bytes, void* stream) {
@@ -136,7 +225,8 @@ int wsvd_latent_decode(const WsvdLatentDecodeParams* p, void* workspace, size_t 
   wsvd::KArgs a;
   fill_args(p, mid_o, lse, sl, ns, &a);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  st = run_stage1(a, s);
+  void* scratch_table = p->rope_table ? nullptr : reinterpret_cast<uint8_t*>(workspace) + partial_bytes(p, ns);
+  st = run_stage1(a, scratch_table, s);
   if (st != WSVD_OK) return st;
   cudaError_t e = wsvd::launch_stage2(mid_o, lse, p->b_seq_len, p->out, p->out_stride_b, p->out_stride_h, p->batch,
                                       p->n_q_heads, ns, p->rank_v, sl, p->wv, p->wv_stride_r, p->n_kv_heads,
@@ -153,7 +243,7 @@ int wsvd_latent_decode_stage1(const WsvdLatentDecodeParams* p, float* mid_o, flo
   if ((long)n_splits * p->split_len < p->max_len) return WSVD_ERR_WORKSPACE_TOO_SMALL;
   wsvd::KArgs a;
   fill_args(p, mid_o, lse, p->split_len, n_splits, &a);
-  return run_stage1(a, reinterpret_cast<cudaStream_t>(stream));
+  return run_stage1(a, nullptr, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int wsvd_decode_stage2(const float* mid_o, const float* lse, const int32_t* b_seq_len, void* out,

@@ -28,12 +28,43 @@ def _need(cond: bool, msg: str, exc=ValueError):
         raise exc(msg)
 
 
-def _cuda_tensor(name, t, dtypes, ndim):
+def _cuda_tensor(name, t, dtypes, ndim, inner_contiguous=True):
     _need(isinstance(t, torch.Tensor), f"{name} must be a torch.Tensor", TypeError)
     _need(t.is_cuda, f"{name} must be a CUDA tensor (no CPU path exists)")
     _need(t.dtype in dtypes, f"{name} has dtype {t.dtype}, expected one of {dtypes}", TypeError)
     _need(t.dim() == ndim, f"{name} must have {ndim} dims, got {tuple(t.shape)}")
-    _need(t.numel() == 0 or t.stride(-1) == 1, f"{name}: innermost dimension must be contiguous")
+    _need(not inner_contiguous or t.numel() == 0 or t.stride(-1) == 1,
+          f"{name}: innermost dimension must be contiguous")
+
+
+_TABLES = {}
+
+
+def rope_table(device, positions: int, head_dim: int = 128, theta: float = 10000.0):
+    """cos/sin position table for the tensor-core kernel, built once per
+    (device, theta, head_dim) and grown geometrically with the longest context seen."""
+    dev = torch.device(device)
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), float(theta), int(head_dim))
+    have = _TABLES.get(key)
+    if have is not None and have[1] >= positions:
+        return have
+    rows = 4096
+    while rows < positions:
+        rows *= 2
+    nbytes = int(_lib.lib().wsvd_rope_table_bytes(rows, head_dim))
+    buf = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        check(_lib.lib().wsvd_rope_table_init(_ptr(buf), nbytes, rows, head_dim, float(theta),
+                                              _stream(None)), "wsvd_rope_table_init")
+    _TABLES[key] = (buf, rows)
+    return _TABLES[key]
+
+
+def kernel_status() -> int:
+    """Status word of the tensor-core kernel (0 = no bounded wait timed out).  Synchronises."""
+    v = ctypes.c_uint32()
+    check(_lib.lib().wsvd_kernel_status(ctypes.byref(v)), "wsvd_kernel_status")
+    return v.value
 
 
 def build_params(
@@ -60,8 +91,8 @@ def build_params(
     _need(wk.shape[0] == Rk, f"wk.shape[0] ({wk.shape[0]}) != rank_k ({Rk})")
     if is_i8:
         _need(k_scale is not None and v_scale is not None, "int8 latents need k_scale and v_scale", TypeError)
-        _cuda_tensor("cache_latent_k_scale", k_scale, (torch.float16,), 2)
-        _cuda_tensor("cache_latent_v_scale", v_scale, (torch.float16,), 2)
+        _cuda_tensor("cache_latent_k_scale", k_scale, (torch.float16,), 2, inner_contiguous=False)
+        _cuda_tensor("cache_latent_v_scale", v_scale, (torch.float16,), 2, inner_contiguous=False)
         _need(k_scale.shape[0] == latent_k.shape[0] and k_scale.shape[1] == Hkv, "k_scale must be [T, Hkv]")
         _need(v_scale.shape[0] == latent_v.shape[0] and v_scale.shape[1] == Hkv, "v_scale must be [T, Hkv]")
     else:
@@ -115,6 +146,9 @@ def build_params(
     p.split_len = int(split_len)
     p.kernel = KERNEL[kernel]
     p.theta, p.sm_scale = float(theta), float(sm_scale)
+    if D == 128 and kernel != "generic":
+        table, rows = rope_table(q.device, int(max_len), D, theta)
+        p.rope_table, p.rope_table_rows = table.data_ptr(), rows
     keep = [q, latent_k, latent_v, k_scale, v_scale, wk, wk_scale, wv, req_to_token, b_req_idx, b_seq_len,
             pos_offset, out]
     return p, keep
