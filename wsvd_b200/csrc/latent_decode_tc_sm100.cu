@@ -18,11 +18,11 @@
 // P.V runs on the CUDA cores in fp32 from the int8 rows.  Nothing is rounded to f16
 // except the two GEMM operands.
 //
-// CTA = one (split, group of 4 heads, sequence); 18 warps:
+// CTA = one (split, group of 4 heads, sequence); 19 warps:
 //   warps 0-15  epilogue, 4 per head: warp w owns tensor-memory lanes 32*(w%4)..+31
-//   warp 16     producer: gathers 64-byte latent rows with 16-byte cp.async through the
+//   warps 16-17 producers: gather 64-byte latent rows with 16-byte cp.async through the
 //               page table into a 5-stage shared-memory ring (16 KB per head-tile)
-//   warp 17     one thread issues the table tile loads (cp.async.bulk) and the MMAs
+//   warp 18     one thread issues the table tile loads (cp.async.bulk) and the MMAs
 // Every wait on an mbarrier is bounded; on a time-out the kernel records a status code
 // and every role falls through to the common exit, which frees the tensor memory.
 #include "common.cuh"
@@ -34,9 +34,10 @@ constexpr int kG = 4;          // heads per CTA
 constexpr int kTile = 128;     // positions per MMA tile (= tensor-memory lanes)
 constexpr int kRk = 64;
 constexpr int kEpiWarps = 4 * kG;
-constexpr int kProducerWarp = kEpiWarps;
-constexpr int kMmaWarp = kEpiWarps + 1;
-constexpr int kThreads = (kEpiWarps + 2) * 32;
+constexpr int kProducerWarps = 2;                 // producer warp w loads heads w, w+2
+constexpr int kProducerWarp0 = kEpiWarps;
+constexpr int kMmaWarp = kEpiWarps + kProducerWarps;
+constexpr int kThreads = (kEpiWarps + kProducerWarps + 1) * 32;
 constexpr int kStages = 5;
 constexpr uint32_t kKBytes = kTile * 64;            // one head-tile of K rows
 constexpr uint32_t kUnitBytes = 2 * kKBytes;        // K rows + V rows (padded to 64 B)
@@ -60,6 +61,17 @@ constexpr uint32_t kSmemBytes = kOffTmemSlot + 16 + 1024;  // + slack for the ma
 enum Status : unsigned int { kOk = 0, kTimeoutProducer = 1, kTimeoutMma = 2, kTimeoutEpilogue = 3 };
 
 __device__ unsigned int g_status = 0;
+
+// Optional cycle-stamp trace of one CTA (compile with -DWSVD_TC_TRACE): role x tile x event.
+#ifdef WSVD_TC_TRACE
+__device__ long long g_trace[4][64][8];
+#define WSVD_TRACE(role, t, ev)                                                         \
+  do {                                                                                  \
+    if (trace_cta && lane == 0 && (t) < 64) g_trace[role][t][ev] = clock64();          \
+  } while (0)
+#else
+#define WSVD_TRACE(role, t, ev)
+#endif
 
 // ------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -228,6 +240,10 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
   const int gqa = p.n_q_heads / p.n_kv_heads;
   const int Rv = p.rank_v;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef WSVD_TC_TRACE
+  const bool trace_cta = blockIdx.x == 1 && blockIdx.y == 1 && blockIdx.z == 1;
+  if (warp == 0) WSVD_TRACE(3, 0, 0);
+#endif
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -280,22 +296,30 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  if (warp == 0) WSVD_TRACE(3, 0, 1);
 
-  if (warp == kProducerWarp) {
-    // ================================================================= producer
+  if (warp >= kProducerWarp0 && warp < kProducerWarp0 + kProducerWarps) {
+    // ================================================================= producers
+    // Lane (r0 = lane/4, c = lane%4) copies 16-byte chunk c of rows r0 + 8k, k < 16.  The
+    // destination chunk is XOR-swizzled with (row/2)%4 so that both "lane = row" 16-byte
+    // reads (scores) and "quarter-warp = two rows" reads (P.V) are bank-conflict free;
+    // (row/2)%4 does not depend on k, so the destination offsets are immediates.
+    const int pw = warp - kProducerWarp0;
     const int c = lane & 3, r0 = lane >> 2;
     const int vchunks = Rv >> 4;
-    const uint8_t* Kb = reinterpret_cast<const uint8_t*>(p.latent_k);
-    const uint8_t* Vb = reinterpret_cast<const uint8_t*>(p.latent_v);
+    const uint8_t* Kb = reinterpret_cast<const uint8_t*>(p.latent_k) + c * 16;
+    const uint8_t* Vb = reinterpret_cast<const uint8_t*>(p.latent_v) + c * 16;
+    const int kst = (int)p.k_stride_t, vst = (int)p.v_stride_t;
+    const uint32_t doff = r0 * 64 + ((c ^ ((r0 >> 1) & 3)) << 4);
     int32_t slot_cur[16], slot_nxt[16];
 #pragma unroll
     for (int k = 0; k < 16; ++k) {
       const int s = lo + r0 + 8 * k;
       slot_nxt[k] = s < hi ? page[s] : -1;
     }
-    int u = 0;
     bool ok = true;
     for (int t = 0; t < ntiles && ok; ++t) {
+      if (pw == 0) WSVD_TRACE(0, t, 0);
 #pragma unroll
       for (int k = 0; k < 16; ++k) slot_cur[k] = slot_nxt[k];
       if (t + 1 < ntiles) {
@@ -305,7 +329,9 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
           slot_nxt[k] = s < hi ? page[s] : -1;
         }
       }
-      for (int g = 0; g < G; ++g, ++u) {
+      const bool full_tile = lo + (t + 1) * kTile <= hi;
+      for (int g = pw; g < G; g += kProducerWarps) {
+        const int u = t * G + g;
         const int stage = u % kStages;
         if (u >= kStages && !mbar_wait(bar_empty(stage), ((u / kStages) - 1) & 1)) {
           atomicMax(&g_status, (unsigned)kTimeoutProducer);
@@ -313,20 +339,28 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
           break;
         }
         const int hk = (h0 + g) / gqa;
-        const uint8_t* kh = Kb + (int64_t)hk * p.k_stride_h + c * 16;
-        const uint8_t* vh = Vb + (int64_t)hk * p.v_stride_h + c * 16;
-        const uint32_t dK = sRing + stage * kUnitBytes, dV = dK + kKBytes;
+        const uint8_t* kh = Kb + (int64_t)hk * p.k_stride_h;
+        const uint8_t* vh = Vb + (int64_t)hk * p.v_stride_h;
+        const uint32_t dK = sRing + stage * kUnitBytes + doff, dV = dK + kKBytes;
+        if (full_tile) {
 #pragma unroll
-        for (int k = 0; k < 16; ++k) {
-          const int r = r0 + 8 * k;
-          const bool valid = slot_cur[k] >= 0;
-          const int64_t sl = valid ? slot_cur[k] : 0;
-          const uint32_t off = r * 64 + ((c ^ ((r >> 1) & 3)) << 4);
-          cp_async16(dK + off, kh + sl * p.k_stride_t, valid ? 16u : 0u);
-          if (c < vchunks) cp_async16(dV + off, vh + sl * p.v_stride_t, valid ? 16u : 0u);
+          for (int k = 0; k < 16; ++k) cp_async16(dK + k * 512, kh + (int64_t)slot_cur[k] * kst, 16u);
+          if (c < vchunks) {
+#pragma unroll
+            for (int k = 0; k < 16; ++k) cp_async16(dV + k * 512, vh + (int64_t)slot_cur[k] * vst, 16u);
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < 16; ++k) {
+            const bool valid = slot_cur[k] >= 0;  // rows past the end are zero-filled
+            const int64_t sl = valid ? slot_cur[k] : 0;
+            cp_async16(dK + k * 512, kh + sl * kst, valid ? 16u : 0u);
+            if (c < vchunks) cp_async16(dV + k * 512, vh + sl * vst, valid ? 16u : 0u);
+          }
         }
         cp_async_arrive_noinc(bar_full(stage));
       }
+      if (pw == 0) WSVD_TRACE(0, t, 1);
     }
     cp_async_wait_all();
   } else if (warp == kMmaWarp) {
@@ -346,8 +380,11 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       bool ok = mbar_wait(bar_pq, 0);
       for (int t = 0; t < ntiles && ok; ++t) {
         const int buf = t & 1;
+        WSVD_TRACE(1, t, 0);
         ok = mbar_wait(bar_a_full(buf), (t >> 1) & 1);
+        WSVD_TRACE(1, t, 1);
         if (ok && t >= 2) ok = mbar_wait(bar_w_empty(buf), ((t >> 1) - 1) & 1);
+        WSVD_TRACE(1, t, 2);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem + buf * (kG * kRk);
@@ -360,10 +397,12 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
         }
         umma_commit(bar_w_full(buf));
         umma_commit(bar_a_empty(buf));
+        WSVD_TRACE(1, t, 3);
         if (t + 1 < ntiles && t + 1 >= 2) {
           ok = mbar_wait(bar_a_empty((t + 1) & 1), (((t + 1) >> 1) - 1) & 1);
           if (ok) issue_table(t + 1);
         }
+        WSVD_TRACE(1, t, 4);
       }
       if (!ok) atomicMax(&g_status, (unsigned)kTimeoutMma);
     }
@@ -380,28 +419,55 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
     {
       const float* qg = qs + g * 128;
       const int tid = threadIdx.x & 127;
+      const int64_t col = (int64_t)hk * 128;
+      const bool vec = p.wk_dtype == WSVD_F16 && (p.wk_stride_r & 7) == 0 &&
+                       (reinterpret_cast<uintptr_t>(p.wk) & 15) == 0;
       for (int task = tid; task < 64 * 8; task += 128) {
         const int r = task >> 3, ic = task & 7;  // rank, chunk of 8 frequencies
+        float u0[8], u1[8];
+        if (vec) {
+          // half layout: dims ic*8.. and 64+ic*8..; interleaved: 16 consecutive dims
+          const __half* w = reinterpret_cast<const __half*>(p.wk) + (int64_t)r * p.wk_stride_r + col;
+          const uint4 a0 = *reinterpret_cast<const uint4*>(w + (interleaved ? ic * 16 : ic * 8));
+          const uint4 a1 = *reinterpret_cast<const uint4*>(w + (interleaved ? ic * 16 + 8 : 64 + ic * 8));
+          const __half* h0p = reinterpret_cast<const __half*>(&a0);
+          const __half* h1p = reinterpret_cast<const __half*>(&a1);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            if (interleaved) {
+              const __half* src = e < 4 ? h0p : h1p;
+              u0[e] = __half2float(src[(2 * e) & 7]);
+              u1[e] = __half2float(src[(2 * e + 1) & 7]);
+            } else {
+              u0[e] = __half2float(h0p[e]);
+              u1[e] = __half2float(h1p[e]);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int i = ic * 8 + e;
+            const int d0 = interleaved ? 2 * i : i, d1 = interleaved ? 2 * i + 1 : i + 64;
+            if (p.wk_dtype == WSVD_I8) {
+              const int8_t* w = reinterpret_cast<const int8_t*>(p.wk) + (int64_t)r * p.wk_stride_r + col;
+              const __half* ws = reinterpret_cast<const __half*>(p.wk_scale) + col;
+              u0[e] = (float)w[d0] * __half2float(ws[d0]);
+              u1[e] = (float)w[d1] * __half2float(ws[d1]);
+            } else {
+              const __half* w = reinterpret_cast<const __half*>(p.wk) + (int64_t)r * p.wk_stride_r + col;
+              u0[e] = __half2float(w[d0]);
+              u1[e] = __half2float(w[d1]);
+            }
+          }
+        }
         __align__(16) __half pv[8];
         __align__(16) __half qv[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const int i = ic * 8 + e;
           const int d0 = interleaved ? 2 * i : i, d1 = interleaved ? 2 * i + 1 : i + 64;
-          const int64_t col = (int64_t)hk * 128;
-          float u0, u1;
-          if (p.wk_dtype == WSVD_I8) {
-            const int8_t* w = reinterpret_cast<const int8_t*>(p.wk) + (int64_t)r * p.wk_stride_r + col;
-            const __half* ws = reinterpret_cast<const __half*>(p.wk_scale) + col;
-            u0 = (float)w[d0] * __half2float(ws[d0]);
-            u1 = (float)w[d1] * __half2float(ws[d1]);
-          } else {
-            const __half* w = reinterpret_cast<const __half*>(p.wk) + (int64_t)r * p.wk_stride_r + col;
-            u0 = __half2float(w[d0]);
-            u1 = __half2float(w[d1]);
-          }
-          pv[e] = __float2half_rn(qg[d0] * u0 + qg[d1] * u1);
-          qv[e] = __float2half_rn(qg[d1] * u0 - qg[d0] * u1);
+          pv[e] = __float2half_rn(qg[d0] * u0[e] + qg[d1] * u1[e]);
+          qv[e] = __float2half_rn(qg[d1] * u0[e] - qg[d0] * u1[e]);
         }
         const int nrow = g * 64 + r;
         const uint32_t off = nrow * 128 + ((ic ^ (nrow & 7)) << 4);
@@ -412,14 +478,18 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_pq);
     }
+    if (warp == 0) WSVD_TRACE(3, 0, 2);
 
     const __half* ksc = reinterpret_cast<const __half*>(p.k_scale) + (int64_t)hk * p.ks_stride_h;
     const __half* vsc = reinterpret_cast<const __half*>(p.v_scale) + (int64_t)hk * p.vs_stride_h;
-    auto load_scales = [&](int s, float& sk, float& sv) {
-      if (s < hi) {
-        const int64_t sl = page[s];
-        sk = __half2float(ksc[sl * p.ks_stride_t]);
-        sv = __half2float(vsc[sl * p.vs_stride_t]);
+    // Scales are read straight from global memory by the lane that owns the token, two
+    // tiles deep: the page entry of tile t+2 and the scales of tile t+1 are requested at
+    // the top of iteration t, so no load is waited on in the iteration that issues it.
+    auto load_slot = [&](int s) -> int { return s < hi ? page[s] : -1; };
+    auto load_scales = [&](int sl, float& sk, float& sv) {
+      if (sl >= 0) {
+        sk = __half2float(ksc[(int64_t)sl * p.ks_stride_t]);
+        sv = __half2float(vsc[(int64_t)sl * p.vs_stride_t]);
       } else {
         sk = 0.f;
         sv = 0.f;
@@ -431,7 +501,8 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
 #pragma unroll
     for (int e = 0; e < 8; ++e) acc[e] = 0ull;
     float sk, sv, sk_n = 0.f, sv_n = 0.f;
-    load_scales(lo + row, sk, sv);
+    load_scales(load_slot(lo + row), sk, sv);
+    int slot_n = load_slot(lo + kTile + row);
     const int rg = lane & 3, tg = lane >> 2;
     const bool pv_on = rg < (Rv >> 4);
     bool ok = true;
@@ -440,37 +511,55 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       const int s = lo + t * kTile + row;
       const bool valid = s < hi;
       const int u = t * G + g, stage = u % kStages, buf = t & 1;
-      if (t + 1 < ntiles) load_scales(s + kTile, sk_n, sv_n);
-      ok = mbar_wait(bar_full(stage), (u / kStages) & 1) && mbar_wait(bar_w_full(buf), (t >> 1) & 1);
+      if (warp == 0) WSVD_TRACE(2, t, 0);
+      load_scales(slot_n, sk_n, sv_n);
+      slot_n = load_slot(s + 2 * kTile);
+      if (warp == 0) WSVD_TRACE(2, t, 1);
+      ok = mbar_wait(bar_full(stage), (u / kStages) & 1);
+      if (warp == 0) WSVD_TRACE(2, t, 2);
+      ok = ok && mbar_wait(bar_w_full(buf), (t >> 1) & 1);
+      if (warp == 0) WSVD_TRACE(2, t, 3);
       if (!ok) break;
       tc_fence_after();
 
-      // ---- score: dot of this token's int8 K row with its row of W
+      // ---- score: dot of this token's int8 K row with its row of W, in two halves of 32
+      //      ranks, four independent accumulators
       const uint32_t krow = sRing + stage * kUnitBytes + row * 64;
       const uint32_t sw = (row >> 1) & 3;
       const uint32_t taddr = tmem + ((uint32_t)(q4 * 32) << 16) + buf * (kG * kRk) + g * kRk;
-      uint64_t dot2 = 0ull;
+      uint64_t dot[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t w[16];
-        tmem_ld16(taddr + c * 16, w);
-        uint4 kw;
-        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                     : "=r"(kw.x), "=r"(kw.y), "=r"(kw.z), "=r"(kw.w)
-                     : "r"(krow + ((c ^ sw) << 4)));
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t w[2][16];
+        uint4 kw[2];
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c = 2 * hf + cc;
+          tmem_ld16(taddr + c * 16, w[cc]);
+          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(kw[cc].x), "=r"(kw[cc].y), "=r"(kw[cc].z), "=r"(kw[cc].w)
+                       : "r"(krow + ((c ^ sw) << 4)));
+        }
         tmem_wait_ld();
-        const uint32_t kws[4] = {kw.x ^ 0x80808080u, kw.y ^ 0x80808080u, kw.z ^ 0x80808080u, kw.w ^ 0x80808080u};
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint64_t x01, x23;
-          cvt4(kws[j], x01, x23);
-          dot2 = fma2(x01, pk(__uint_as_float(w[4 * j]), __uint_as_float(w[4 * j + 1])), dot2);
-          dot2 = fma2(x23, pk(__uint_as_float(w[4 * j + 2]), __uint_as_float(w[4 * j + 3])), dot2);
+        for (int cc = 0; cc < 2; ++cc) {
+          const uint32_t kws[4] = {kw[cc].x ^ 0x80808080u, kw[cc].y ^ 0x80808080u, kw[cc].z ^ 0x80808080u,
+                                   kw[cc].w ^ 0x80808080u};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint64_t x01, x23;
+            cvt4(kws[j], x01, x23);
+            dot[2 * cc] = fma2(x01, pk(__uint_as_float(w[cc][4 * j]), __uint_as_float(w[cc][4 * j + 1])), dot[2 * cc]);
+            dot[2 * cc + 1] =
+                fma2(x23, pk(__uint_as_float(w[cc][4 * j + 2]), __uint_as_float(w[cc][4 * j + 3])), dot[2 * cc + 1]);
+          }
         }
       }
+      const uint64_t dot2 = add2(add2(dot[0], dot[1]), add2(dot[2], dot[3]));
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_w_empty(buf));
+      if (warp == 0) WSVD_TRACE(2, t, 4);
       float d0, d1;
       upk(dot2, d0, d1);
       const float z = valid ? (d0 + d1) * sk : -INFINITY;
@@ -488,6 +577,7 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       const float pr = valid ? fast_exp2(z - m_w) : 0.f;
       l_lane += pr;
       const float pvs = pr * sv;
+      if (warp == 0) WSVD_TRACE(2, t, 5);
 
       // ---- P.V on the CUDA cores: this lane owns 16 ranks (chunk rg) of tokens tg + 8k
       const uint32_t vbase = sRing + stage * kUnitBytes + kKBytes + (q4 * 32) * 64;
@@ -514,6 +604,7 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_empty(stage));
+      if (warp == 0) WSVD_TRACE(2, t, 6);
       sk = sk_n;
       sv = sv_n;
     }
@@ -599,6 +690,12 @@ cudaError_t launch_stage1_tc(const KArgs& a, const void* table, int table_rows, 
 cudaError_t read_tc_status(unsigned int* out) {
   return cudaMemcpyFromSymbol(out, tc::g_status, sizeof(unsigned int));
 }
+
+#ifdef WSVD_TC_TRACE
+extern "C" int wsvd_debug_read_trace(long long* dst) {
+  return (int)cudaMemcpyFromSymbol(dst, tc::g_trace, sizeof(long long) * 4 * 64 * 8);
+}
+#endif
 
 cudaError_t reset_tc_status() {
   const unsigned int zero = 0;
