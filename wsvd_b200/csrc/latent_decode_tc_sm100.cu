@@ -34,11 +34,20 @@ constexpr int kG = 4;          // heads per CTA
 constexpr int kTile = 128;     // positions per MMA tile (= tensor-memory lanes)
 constexpr int kRk = 64;
 constexpr int kEpiWarps = 4 * kG;
-constexpr int kProducerWarps = 2;                 // producer warp w loads heads w, w+2
+#ifndef WSVD_TC_PRODUCER_WARPS
+#define WSVD_TC_PRODUCER_WARPS 2
+#endif
+constexpr int kProducerWarps = WSVD_TC_PRODUCER_WARPS;  // even: K rows, odd: V rows; split further by row range
+constexpr int kRowSplit = kProducerWarps / 2;            // producers per tensor
+constexpr int kKPerLane = 16 / kRowSplit;                 // rows per lane per head-tile
 constexpr int kProducerWarp0 = kEpiWarps;
 constexpr int kMmaWarp = kEpiWarps + kProducerWarps;
 constexpr int kThreads = (kEpiWarps + kProducerWarps + 1) * 32;
 constexpr int kStages = 5;
+#ifndef WSVD_TC_PREFETCH_TILES
+#define WSVD_TC_PREFETCH_TILES 3
+#endif
+constexpr int kPrefetchTiles = WSVD_TC_PREFETCH_TILES;   // latent rows are requested into L2 this many tiles ahead
 constexpr uint32_t kKBytes = kTile * 64;            // one head-tile of K rows
 constexpr uint32_t kUnitBytes = 2 * kKBytes;        // K rows + V rows (padded to 64 B)
 constexpr uint32_t kAHalfBytes = kTile * 128;       // 128 rows x 64 f16
@@ -64,7 +73,7 @@ __device__ unsigned int g_status = 0;
 
 // Optional cycle-stamp trace of one CTA (compile with -DWSVD_TC_TRACE): role x tile x event.
 #ifdef WSVD_TC_TRACE
-__device__ long long g_trace[4][64][8];
+__device__ long long g_trace[8][64][8];
 #define WSVD_TRACE(role, t, ev)                                                         \
   do {                                                                                  \
     if (trace_cta && lane == 0 && (t) < 64) g_trace[role][t][ev] = clock64();          \
@@ -85,12 +94,18 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// try_wait with a suspend-time hint: the waiting thread is parked by the hardware until
+// the phase completes or the hint (ns) expires, instead of spinning on issue slots that
+// the producer and MMA warps need.
+#ifndef WSVD_TC_WAIT_HINT_NS
+#define WSVD_TC_WAIT_HINT_NS 20000
+#endif
 __device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
-      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"((uint32_t)WSVD_TC_WAIT_HINT_NS)
       : "memory");
   return ok;
 }
@@ -115,6 +130,9 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32
 }
 __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void prefetch_l2_bulk(const void* p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -242,7 +260,7 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #ifdef WSVD_TC_TRACE
   const bool trace_cta = blockIdx.x == 1 && blockIdx.y == 1 && blockIdx.z == 1;
-  if (warp == 0) WSVD_TRACE(3, 0, 0);
+  if (warp == 0) WSVD_TRACE(7, 0, 0);
 #endif
 
   extern __shared__ uint8_t smem_raw[];
@@ -268,7 +286,7 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
   if (warp == kMmaWarp) {
     if (lane == 0) {
       for (int s = 0; s < kStages; ++s) {
-        mbar_init(bar_full(s), 32);   // one asynchronous arrive per producer lane
+        mbar_init(bar_full(s), 32 * kProducerWarps);   // one asynchronous arrive per producer lane
         mbar_init(bar_empty(s), 4);   // one arrive per epilogue warp of the owning head
       }
       for (int i = 0; i < 2; ++i) {
@@ -296,69 +314,86 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  if (warp == 0) WSVD_TRACE(3, 0, 1);
+  if (warp == 0) WSVD_TRACE(7, 0, 1);
 
   if (warp >= kProducerWarp0 && warp < kProducerWarp0 + kProducerWarps) {
     // ================================================================= producers
+    // Producer 0 copies the K rows and producer 1 the V rows of every head-tile, so both
+    // walk the ring in the same order (a waiter can then never be two phases ahead of an
+    // mbarrier, which a parity wait could not tell from "done").
     // Lane (r0 = lane/4, c = lane%4) copies 16-byte chunk c of rows r0 + 8k, k < 16.  The
     // destination chunk is XOR-swizzled with (row/2)%4 so that both "lane = row" 16-byte
     // reads (scores) and "quarter-warp = two rows" reads (P.V) are bank-conflict free;
     // (row/2)%4 does not depend on k, so the destination offsets are immediates.
     const int pw = warp - kProducerWarp0;
-    const int c = lane & 3, r0 = lane >> 2;
-    const int vchunks = Rv >> 4;
-    const uint8_t* Kb = reinterpret_cast<const uint8_t*>(p.latent_k) + c * 16;
-    const uint8_t* Vb = reinterpret_cast<const uint8_t*>(p.latent_v) + c * 16;
-    const int kst = (int)p.k_stride_t, vst = (int)p.v_stride_t;
-    const uint32_t doff = r0 * 64 + ((c ^ ((r0 >> 1) & 3)) << 4);
-    int32_t slot_cur[16], slot_nxt[16];
+    const int is_v = pw & 1, kbase = (pw >> 1) * kKPerLane;
+    const int c = lane & 3, r0 = (lane >> 2) + 8 * kbase;
+    const bool chunk_on = !is_v || c < (Rv >> 4);
+    const uint8_t* base = reinterpret_cast<const uint8_t*>(is_v ? p.latent_v : p.latent_k) + c * 16;
+    const int64_t hstride = is_v ? p.v_stride_h : p.k_stride_h;
+    const int tstride = (int)(is_v ? p.v_stride_t : p.k_stride_t);
+    const uint32_t doff = (is_v ? kKBytes : 0u) + r0 * 64 + ((c ^ ((r0 >> 1) & 3)) << 4);
+    int32_t slot_cur[kKPerLane], slot_nxt[kKPerLane];
 #pragma unroll
-    for (int k = 0; k < 16; ++k) {
+    for (int k = 0; k < kKPerLane; ++k) {
       const int s = lo + r0 + 8 * k;
-      slot_nxt[k] = s < hi ? page[s] : -1;
+      slot_nxt[k] = -1;
+      if (s < hi) slot_nxt[k] = page[s];
     }
     bool ok = true;
+    int u = 0;
     for (int t = 0; t < ntiles && ok; ++t) {
       if (pw == 0) WSVD_TRACE(0, t, 0);
 #pragma unroll
-      for (int k = 0; k < 16; ++k) slot_cur[k] = slot_nxt[k];
+      for (int k = 0; k < kKPerLane; ++k) slot_cur[k] = slot_nxt[k];
       if (t + 1 < ntiles) {
 #pragma unroll
-        for (int k = 0; k < 16; ++k) {
+        for (int k = 0; k < kKPerLane; ++k) {
           const int s = lo + (t + 1) * kTile + r0 + 8 * k;
-          slot_nxt[k] = s < hi ? page[s] : -1;
+          slot_nxt[k] = -1;
+          if (s < hi) slot_nxt[k] = page[s];
         }
       }
       const bool full_tile = lo + (t + 1) * kTile <= hi;
-      for (int g = pw; g < G; g += kProducerWarps) {
-        const int u = t * G + g;
+      for (int g = 0; g < G; ++g, ++u) {
         const int stage = u % kStages;
+        if (pw == 0) WSVD_TRACE(6, u, 0);
         if (u >= kStages && !mbar_wait(bar_empty(stage), ((u / kStages) - 1) & 1)) {
           atomicMax(&g_status, (unsigned)kTimeoutProducer);
           ok = false;
           break;
         }
-        const int hk = (h0 + g) / gqa;
-        const uint8_t* kh = Kb + (int64_t)hk * p.k_stride_h;
-        const uint8_t* vh = Vb + (int64_t)hk * p.v_stride_h;
-        const uint32_t dK = sRing + stage * kUnitBytes + doff, dV = dK + kKBytes;
-        if (full_tile) {
+        if (pw == 0) WSVD_TRACE(6, u, 1);
+        const uint8_t* src = base + (int64_t)((h0 + g) / gqa) * hstride;
+        const uint32_t dst = sRing + stage * kUnitBytes + doff;
+        if (chunk_on) {
+          if (full_tile) {
 #pragma unroll
-          for (int k = 0; k < 16; ++k) cp_async16(dK + k * 512, kh + (int64_t)slot_cur[k] * kst, 16u);
-          if (c < vchunks) {
+            for (int k = 0; k < kKPerLane; ++k) cp_async16(dst + k * 512, src + (int64_t)slot_cur[k] * tstride, 16u);
+          } else {
 #pragma unroll
-            for (int k = 0; k < 16; ++k) cp_async16(dV + k * 512, vh + (int64_t)slot_cur[k] * vst, 16u);
-          }
-        } else {
-#pragma unroll
-          for (int k = 0; k < 16; ++k) {
-            const bool valid = slot_cur[k] >= 0;  // rows past the end are zero-filled
-            const int64_t sl = valid ? slot_cur[k] : 0;
-            cp_async16(dK + k * 512, kh + sl * kst, valid ? 16u : 0u);
-            if (c < vchunks) cp_async16(dV + k * 512, vh + sl * vst, valid ? 16u : 0u);
+            for (int k = 0; k < kKPerLane; ++k) {
+              const bool valid = slot_cur[k] >= 0;  // rows past the end are zero-filled
+              cp_async16(dst + k * 512, src + (int64_t)(valid ? slot_cur[k] : 0) * tstride, valid ? 16u : 0u);
+            }
           }
         }
+        if (pw == 0) WSVD_TRACE(6, u, 3);
         cp_async_arrive_noinc(bar_full(stage));
+        if (pw == 0) WSVD_TRACE(6, u, 2);
+      }
+      // Ask for the rows of tile t + kPrefetchTiles to be brought into L2 (one bulk
+      // prefetch per head when the 128 rows are contiguous in memory) so that the ring
+      // only has to cover the L2 -> shared-memory latency, not the DRAM latency.
+      if (kPrefetchTiles > 0 && pw < 2 && lane == 0 && t + kPrefetchTiles < ntiles) {
+        const int s0 = lo + (t + kPrefetchTiles) * kTile;
+        const int rows = min(kTile, hi - s0);
+        const int rowbytes = is_v ? Rv : kRk;
+        if (tstride == rowbytes && page[s0 + rows - 1] - page[s0] == rows - 1) {
+          const int64_t sl0 = page[s0];
+          for (int g = 0; g < G; ++g)
+            prefetch_l2_bulk(base - c * 16 + (int64_t)((h0 + g) / gqa) * hstride + sl0 * tstride, rows * rowbytes);
+        }
       }
       if (pw == 0) WSVD_TRACE(0, t, 1);
     }
@@ -478,21 +513,23 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_pq);
     }
-    if (warp == 0) WSVD_TRACE(3, 0, 2);
+    if (warp == 0) WSVD_TRACE(7, 0, 2);
 
     const __half* ksc = reinterpret_cast<const __half*>(p.k_scale) + (int64_t)hk * p.ks_stride_h;
     const __half* vsc = reinterpret_cast<const __half*>(p.v_scale) + (int64_t)hk * p.vs_stride_h;
     // Scales are read straight from global memory by the lane that owns the token, two
     // tiles deep: the page entry of tile t+2 and the scales of tile t+1 are requested at
     // the top of iteration t, so no load is waited on in the iteration that issues it.
-    auto load_slot = [&](int s) -> int { return s < hi ? page[s] : -1; };
-    auto load_scales = [&](int sl, float& sk, float& sv) {
+    auto load_slot = [&](int s, int& sl) {
+      sl = -1;
+      if (s < hi) sl = page[s];  // predicated load: nothing consumes the value here
+    };
+    auto load_scales = [&](int sl, unsigned short& sk, unsigned short& sv) {
+      sk = 0;
+      sv = 0;
       if (sl >= 0) {
-        sk = __half2float(ksc[(int64_t)sl * p.ks_stride_t]);
-        sv = __half2float(vsc[(int64_t)sl * p.vs_stride_t]);
-      } else {
-        sk = 0.f;
-        sv = 0.f;
+        sk = reinterpret_cast<const unsigned short*>(ksc)[(int64_t)sl * p.ks_stride_t];
+        sv = reinterpret_cast<const unsigned short*>(vsc)[(int64_t)sl * p.vs_stride_t];
       }
     };
 
@@ -500,9 +537,11 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
     uint64_t acc[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) acc[e] = 0ull;
-    float sk, sv, sk_n = 0.f, sv_n = 0.f;
-    load_scales(load_slot(lo + row), sk, sv);
-    int slot_n = load_slot(lo + kTile + row);
+    unsigned short sk_raw, sv_raw, sk_n = 0, sv_n = 0;
+    int slot_n;
+    load_slot(lo + row, slot_n);
+    load_scales(slot_n, sk_raw, sv_raw);
+    load_slot(lo + kTile + row, slot_n);
     const int rg = lane & 3, tg = lane >> 2;
     const bool pv_on = rg < (Rv >> 4);
     bool ok = true;
@@ -511,14 +550,14 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       const int s = lo + t * kTile + row;
       const bool valid = s < hi;
       const int u = t * G + g, stage = u % kStages, buf = t & 1;
-      if (warp == 0) WSVD_TRACE(2, t, 0);
+      if (q4 == 0) WSVD_TRACE(2 + g, t, 0);
       load_scales(slot_n, sk_n, sv_n);
-      slot_n = load_slot(s + 2 * kTile);
-      if (warp == 0) WSVD_TRACE(2, t, 1);
+      load_slot(s + 2 * kTile, slot_n);
+      if (q4 == 0) WSVD_TRACE(2 + g, t, 1);
       ok = mbar_wait(bar_full(stage), (u / kStages) & 1);
-      if (warp == 0) WSVD_TRACE(2, t, 2);
+      if (q4 == 0) WSVD_TRACE(2 + g, t, 2);
       ok = ok && mbar_wait(bar_w_full(buf), (t >> 1) & 1);
-      if (warp == 0) WSVD_TRACE(2, t, 3);
+      if (q4 == 0) WSVD_TRACE(2 + g, t, 3);
       if (!ok) break;
       tc_fence_after();
 
@@ -559,9 +598,10 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_w_empty(buf));
-      if (warp == 0) WSVD_TRACE(2, t, 4);
+      if (q4 == 0) WSVD_TRACE(2 + g, t, 4);
       float d0, d1;
       upk(dot2, d0, d1);
+      const float sk = __half2float(__ushort_as_half(sk_raw)), sv = __half2float(__ushort_as_half(sv_raw));
       const float z = valid ? (d0 + d1) * sk : -INFINITY;
 
       // ---- online softmax, per warp
@@ -577,7 +617,7 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       const float pr = valid ? fast_exp2(z - m_w) : 0.f;
       l_lane += pr;
       const float pvs = pr * sv;
-      if (warp == 0) WSVD_TRACE(2, t, 5);
+      if (q4 == 0) WSVD_TRACE(2 + g, t, 5);
 
       // ---- P.V on the CUDA cores: this lane owns 16 ranks (chunk rg) of tokens tg + 8k
       const uint32_t vbase = sRing + stage * kUnitBytes + kKBytes + (q4 * 32) * 64;
@@ -604,9 +644,9 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_empty(stage));
-      if (warp == 0) WSVD_TRACE(2, t, 6);
-      sk = sk_n;
-      sv = sv_n;
+      if (q4 == 0) WSVD_TRACE(2 + g, t, 6);
+      sk_raw = sk_n;
+      sv_raw = sv_n;
     }
     if (!ok) atomicMax(&g_status, (unsigned)kTimeoutEpilogue);
 
@@ -693,7 +733,7 @@ cudaError_t read_tc_status(unsigned int* out) {
 
 #ifdef WSVD_TC_TRACE
 extern "C" int wsvd_debug_read_trace(long long* dst) {
-  return (int)cudaMemcpyFromSymbol(dst, tc::g_trace, sizeof(long long) * 4 * 64 * 8);
+  return (int)cudaMemcpyFromSymbol(dst, tc::g_trace, sizeof(long long) * 8 * 64 * 8);
 }
 #endif
 
