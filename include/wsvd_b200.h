@@ -77,6 +77,8 @@ typedef struct WsvdLatentDecodeParams {
   float sm_scale;           /* 0 = 1/sqrt(head_dim) (stage1.py:244) */
   const void* rope_table;   /* optional: table made by wsvd_rope_table_init for the same theta/head_dim */
   int32_t rope_table_rows;  /* positions it covers (>= max_len rounded up to 128) */
+  int64_t n_token_slots;    /* T, the extent of latent_k/v along the token-slot axis; 0 = unknown (the
+                               tensor-core kernel then gathers rows with cp.async instead of TMA) */
 } WsvdLatentDecodeParams;
 
 /* Version of this header the library was built from. */

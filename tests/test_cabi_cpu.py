@@ -1,0 +1,112 @@
+"""The C-ABI library on a machine without a GPU: it loads, exports every symbol that
+include/wsvd_b200.h declares, and rejects bad arguments with status codes before any
+CUDA call is made."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from wsvd_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "wsvd_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(wsvd_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported_and_bound():
+    lib = _lib.lib()
+    names = _declared_symbols()
+    assert len(names) >= 10
+    for name in names:
+        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+        assert name in _lib.SYMBOLS, f"{name} has no ctypes prototype"
+
+
+def test_abi_version_and_status_strings():
+    lib = _lib.lib()
+    assert lib.wsvd_abi_version() == 1
+    for code in range(0, 9):
+        assert lib.wsvd_status_string(code)
+    assert lib.wsvd_status_string(0) == b"ok"
+    assert b"unknown" in lib.wsvd_status_string(99)
+
+
+def _params(**kw):
+    p = _lib.LatentDecodeParams()
+    fake = 0x1000  # never dereferenced on the host: validation only looks at NULL-ness
+    for f in ("q", "latent_k", "latent_v", "k_scale", "v_scale", "wk", "req_to_token", "b_req_idx", "b_seq_len", "out"):
+        setattr(p, f, fake)
+    p.batch, p.n_q_heads, p.n_kv_heads, p.head_dim, p.rank_k, p.rank_v = 2, 8, 8, 128, 64, 64
+    p.max_len, p.latent_dtype, p.wk_dtype, p.theta = 1000, 0, 1, 10000.0
+    for k, v in kw.items():
+        setattr(p, k, v)
+    return p
+
+
+@pytest.mark.parametrize("field,value,status", [
+    ("q", None, 1), ("latent_k", None, 1), ("b_seq_len", None, 1), ("out", None, 1),
+    ("head_dim", 96, 2), ("n_kv_heads", 3, 2), ("rank_k", 0, 2), ("rank_v", 129, 2), ("batch", -1, 2),
+    ("latent_dtype", 7, 3), ("k_scale", None, 3), ("rope_layout", 5, 3), ("kernel", 9, 3),
+    ("batch", 70000, 8), ("theta", 0.0, 2),
+])
+def test_validation_status_codes(field, value, status):
+    lib = _lib.lib()
+    p = _params(**{field: value})
+    ws = ctypes.c_void_p(0x2000)
+    assert lib.wsvd_latent_decode(ctypes.byref(p), ws, 1 << 30, None) == status
+
+
+def test_int8_wk_needs_scale_and_workspace_checks():
+    lib = _lib.lib()
+    p = _params(wk_dtype=0)
+    assert lib.wsvd_latent_decode(ctypes.byref(p), ctypes.c_void_p(0x2000), 1 << 30, None) == 3
+    p = _params()
+    need = lib.wsvd_latent_decode_workspace_bytes(ctypes.byref(p))
+    assert need > 0
+    assert lib.wsvd_latent_decode(ctypes.byref(p), None, need, None) == 1
+    assert lib.wsvd_latent_decode(ctypes.byref(p), ctypes.c_void_p(0x2000), need - 1, None) == 5
+    assert lib.wsvd_latent_decode(ctypes.byref(p), ctypes.c_void_p(0x2001), need, None) == 4
+    assert lib.wsvd_latent_decode(None, ctypes.c_void_p(0x2000), need, None) == 1
+
+
+def test_split_plan_is_consistent_with_workspace_size():
+    lib = _lib.lib()
+    for max_len, split in [(1, 0), (127, 0), (8192, 0), (32768, 0), (5000, 256), (5000, 1024)]:
+        for kernel in (0, 1):
+            p = _params(max_len=max_len, split_len=split, kernel=kernel)
+            sl, ns = ctypes.c_int32(), ctypes.c_int32()
+            assert lib.wsvd_latent_decode_plan(ctypes.byref(p), ctypes.byref(sl), ctypes.byref(ns)) == 0
+            assert sl.value > 0 and ns.value * sl.value >= max_len and (ns.value - 1) * sl.value < max(max_len, 1)
+            if split:
+                assert sl.value == split
+            need = lib.wsvd_latent_decode_workspace_bytes(ctypes.byref(p))
+            assert need >= p.batch * p.n_q_heads * ns.value * (p.rank_v + 1) * 4
+
+
+def test_empty_batch_is_a_no_op():
+    lib = _lib.lib()
+    p = _params(batch=0)
+    assert lib.wsvd_latent_decode(ctypes.byref(p), None, 0, None) == 0
+
+
+def test_rope_table_size_and_argument_checks():
+    lib = _lib.lib()
+    assert lib.wsvd_rope_table_bytes(8192, 128) == 8192 * 256
+    assert lib.wsvd_rope_table_bytes(1, 128) == 128 * 256
+    assert lib.wsvd_rope_table_bytes(8192, 64) == 0
+    assert lib.wsvd_rope_table_init(None, 0, 128, 128, 1e4, None) == 1
+    assert lib.wsvd_rope_table_init(ctypes.c_void_p(0x1000), 10, 128, 128, 1e4, None) == 5
+    assert lib.wsvd_rope_table_init(ctypes.c_void_p(0x1000), 1 << 20, 128, 64, 1e4, None) == 7
+
+
+def test_stage2_argument_checks():
+    lib = _lib.lib()
+    f = ctypes.c_void_p(0x1000)
+    assert lib.wsvd_decode_stage2(None, f, f, f, 64, 64, 1, 1, 1, 64, 256, None, 0, 1, 0, None) == 1
+    assert lib.wsvd_decode_stage2(f, f, f, f, 64, 64, 1, 1, 1, 200, 256, None, 0, 1, 0, None) == 2
+    assert lib.wsvd_decode_stage2(f, f, f, f, 64, 64, 0, 1, 1, 64, 256, None, 0, 1, 0, None) == 0

@@ -86,6 +86,7 @@ class LatentDecodeParams(ctypes.Structure):
         ("split_len", ctypes.c_int32), ("kernel", ctypes.c_int32),
         ("theta", ctypes.c_float), ("sm_scale", ctypes.c_float),
         ("rope_table", ctypes.c_void_p), ("rope_table_rows", ctypes.c_int32),
+        ("n_token_slots", ctypes.c_int64),
     ]
 
 

@@ -14,17 +14,23 @@
 // position table of cos/sin values (f16, shared by every head and sequence, read from
 // L2), the B operand [P;Q] is built once per CTA and stays in shared memory.  The int8
 // latents never pass through the tensor core: each epilogue thread owns one token,
-// reads its row of W from tensor memory and dots it with the token's int8 row in fp32.
-// P.V runs on the CUDA cores in fp32 from the int8 rows.  Nothing is rounded to f16
-// except the two GEMM operands.
+// reads its row of W from tensor memory and dots it with the token's int8 K row (from
+// shared memory) in fp32.  P.V runs on the CUDA cores in fp32 from the int8 V rows.
+// Nothing is rounded to f16 except the two GEMM operands.
 //
-// CTA = one (split, group of 4 heads, sequence); 19 warps:
+// CTA = one (split, group of 4 heads, sequence); 18 warps:
 //   warps 0-15  epilogue, 4 per head: warp w owns tensor-memory lanes 32*(w%4)..+31
-//   warps 16-17 producers: gather 64-byte latent rows with 16-byte cp.async through the
-//               page table into a 5-stage shared-memory ring (16 KB per head-tile)
-//   warp 18     one thread issues the table tile loads (cp.async.bulk) and the MMAs
+//   warp 16     producer of the K and V rows: every head has a ring of three 8 KB slots of
+//               half a tile (64 tokens); two TMA tensor copies per slot when the tile's
+//               token slots are consecutive, else a gather of rows with 16-byte cp.async
+//               through the page table.  A slot is handed back as soon as the score is
+//               computed (the V rows are copied to registers first).
+//   warp 17     one thread issues the table tile loads (cp.async.bulk) and the MMAs
 // Every wait on an mbarrier is bounded; on a time-out the kernel records a status code
 // and every role falls through to the common exit, which frees the tensor memory.
+#include <cuda.h>
+#include <string.h>
+
 #include "common.cuh"
 
 namespace wsvd {
@@ -34,22 +40,19 @@ constexpr int kG = 4;          // heads per CTA
 constexpr int kTile = 128;     // positions per MMA tile (= tensor-memory lanes)
 constexpr int kRk = 64;
 constexpr int kEpiWarps = 4 * kG;
-#ifndef WSVD_TC_PRODUCER_WARPS
-#define WSVD_TC_PRODUCER_WARPS 2
-#endif
-constexpr int kProducerWarps = WSVD_TC_PRODUCER_WARPS;  // even: K rows, odd: V rows; split further by row range
-constexpr int kRowSplit = kProducerWarps / 2;            // producers per tensor
-constexpr int kKPerLane = 16 / kRowSplit;                 // rows per lane per head-tile
+constexpr int kProducerWarps = 1;
 constexpr int kProducerWarp0 = kEpiWarps;
 constexpr int kMmaWarp = kEpiWarps + kProducerWarps;
 constexpr int kThreads = (kEpiWarps + kProducerWarps + 1) * 32;
-constexpr int kStages = 5;
-#ifndef WSVD_TC_PREFETCH_TILES
-#define WSVD_TC_PREFETCH_TILES 3
-#endif
-constexpr int kPrefetchTiles = WSVD_TC_PREFETCH_TILES;   // latent rows are requested into L2 this many tiles ahead
-constexpr uint32_t kKBytes = kTile * 64;            // one head-tile of K rows
-constexpr uint32_t kUnitBytes = 2 * kKBytes;        // K rows + V rows (padded to 64 B)
+// Latent ring: every head owns kSlots slots, each holding half a tile (64 tokens): K rows
+// at a 64-byte pitch followed by V rows at a rank_v pitch.  A slot is only ever reused by
+// the same head, whose warps consume their slots in order; with slots shared between heads
+// a warp could get two phases ahead of a slot's mbarrier, which a parity wait cannot see.
+constexpr int kHalf = kTile / 2;
+constexpr int kSlots = 3;
+constexpr int kStages = kG * kSlots;
+constexpr uint32_t kKBytes = kHalf * 64;            // K rows of one half-tile
+constexpr uint32_t kUnitBytes = 2 * kKBytes;        // + V rows
 constexpr uint32_t kAHalfBytes = kTile * 128;       // 128 rows x 64 f16
 constexpr uint32_t kABufBytes = 2 * kAHalfBytes;    // cos half + sin half
 constexpr uint32_t kBHalfBytes = kG * kRk * 128;    // 256 rows x 64 f16
@@ -59,15 +62,15 @@ constexpr uint32_t kTmemCols = 512;                 // 2 buffers x (kG*kRk) fp32
 constexpr uint32_t kOffB = 0;
 constexpr uint32_t kOffA = kOffB + 2 * kBHalfBytes;
 constexpr uint32_t kOffRing = kOffA + 2 * kABufBytes;
-constexpr uint32_t kOffMerge = kOffRing + kStages * kUnitBytes;
+constexpr uint32_t kOffMerge = kOffB;  // end-of-CTA merge scratch reuses the B operand (all MMAs are done by then)
 constexpr uint32_t kMergeFloats = kG * 4 * (2 + 64);
-constexpr uint32_t kOffQ = kOffMerge + kMergeFloats * 4;
+constexpr uint32_t kOffQ = kOffRing + kStages * kUnitBytes;
 constexpr uint32_t kOffBar = kOffQ + kG * 128 * 4;
 constexpr int kNumBars = 2 * kStages + 2 + 2 + 2 + 2 + 1;
 constexpr uint32_t kOffTmemSlot = kOffBar + kNumBars * 8;
-constexpr uint32_t kSmemBytes = kOffTmemSlot + 16 + 1024;  // + slack for the manual alignment
+constexpr uint32_t kSmemBytes = kOffTmemSlot + 16;  // the dynamic shared-memory base is 1024-byte aligned
 
-enum Status : unsigned int { kOk = 0, kTimeoutProducer = 1, kTimeoutMma = 2, kTimeoutEpilogue = 3 };
+enum Status : unsigned int { kOk = 0, kTimeoutProducer = 1, kTimeoutMma = 2, kTimeoutEpilogue = 3, kBadSmemAlignment = 4 };
 
 __device__ unsigned int g_status = 0;
 
@@ -102,6 +105,14 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 #endif
 __device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
+#ifdef WSVD_TC_TEST_WAIT
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+#endif
   asm volatile(
       "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}"
       : "=r"(ok)
@@ -131,14 +142,17 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32
 __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void prefetch_l2_bulk(const void* p, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                "l"(src), "r"(bytes), "r"(bar)
                : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+      : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
@@ -229,6 +243,13 @@ struct TcArgs {
   KArgs k;
   const uint8_t* table;   // [2][rows][128 B] cos | sin halves, f16, 16-byte chunks XOR-swizzled by row%8
   int32_t table_rows;
+  // TMA descriptors of the K and V latent tensors as 3-D byte tensors (rank, and the
+  // token-slot and head axes ordered by stride).  K rows land with the 64-byte swizzle,
+  // which is the XOR pattern the score loop reads with; V rows land dense.
+  int32_t use_tma;        // 0: rows are gathered with cp.async
+  int32_t slot_axis;      // 1 or 2: which tensor-map coordinate is the token slot
+  alignas(64) CUtensorMap tmap_k;
+  alignas(64) CUtensorMap tmap_v;
 };
 
 // ------------------------------------------------------------------ position table
@@ -263,10 +284,13 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
   if (warp == 0) WSVD_TRACE(7, 0, 0);
 #endif
 
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t sbase = (raw + 1023u) & ~1023u;
-  uint8_t* sm = smem_raw + (sbase - raw);
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t sbase = smem_u32(smem_raw);
+  uint8_t* sm = smem_raw;
+  if ((sbase & 1023u) != 0) {  // the swizzled operand tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) atomicMax(&g_status, (unsigned)kBadSmemAlignment);
+    return;
+  }
   const uint32_t sB = sbase + kOffB, sA = sbase + kOffA, sRing = sbase + kOffRing;
   float* merge = reinterpret_cast<float*>(sm + kOffMerge);
   float* qs = reinterpret_cast<float*>(sm + kOffQ);
@@ -287,7 +311,7 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
     if (lane == 0) {
       for (int s = 0; s < kStages; ++s) {
         mbar_init(bar_full(s), 32 * kProducerWarps);   // one asynchronous arrive per producer lane
-        mbar_init(bar_empty(s), 4);   // one arrive per epilogue warp of the owning head
+        mbar_init(bar_empty(s), 2);   // the two epilogue warps that own the half-tile's tokens
       }
       for (int i = 0; i < 2; ++i) {
         mbar_init(bar_a_full(i), 1);
@@ -318,85 +342,103 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
 
   if (warp >= kProducerWarp0 && warp < kProducerWarp0 + kProducerWarps) {
     // ================================================================= producers
-    // Producer 0 copies the K rows and producer 1 the V rows of every head-tile, so both
-    // walk the ring in the same order (a waiter can then never be two phases ahead of an
-    // mbarrier, which a parity wait could not tell from "done").
-    // Lane (r0 = lane/4, c = lane%4) copies 16-byte chunk c of rows r0 + 8k, k < 16.  The
-    // destination chunk is XOR-swizzled with (row/2)%4 so that both "lane = row" 16-byte
-    // reads (scores) and "quarter-warp = two rows" reads (P.V) are bank-conflict free;
-    // (row/2)%4 does not depend on k, so the destination offsets are immediates.
+    // One warp fills every head's slots, half-tile by half-tile, in order.
     const int pw = warp - kProducerWarp0;
-    const int is_v = pw & 1, kbase = (pw >> 1) * kKPerLane;
-    const int c = lane & 3, r0 = (lane >> 2) + 8 * kbase;
-    const bool chunk_on = !is_v || c < (Rv >> 4);
-    const uint8_t* base = reinterpret_cast<const uint8_t*>(is_v ? p.latent_v : p.latent_k) + c * 16;
-    const int64_t hstride = is_v ? p.v_stride_h : p.k_stride_h;
-    const int tstride = (int)(is_v ? p.v_stride_t : p.k_stride_t);
-    const uint32_t doff = (is_v ? kKBytes : 0u) + r0 * 64 + ((c ^ ((r0 >> 1) & 3)) << 4);
-    int32_t slot_cur[kKPerLane], slot_nxt[kKPerLane];
+    const uint8_t* kbase = reinterpret_cast<const uint8_t*>(p.latent_k);
+    const uint8_t* vbase_g = reinterpret_cast<const uint8_t*>(p.latent_v);
+    const int kst = (int)p.k_stride_t, vst = (int)p.v_stride_t;
+    const uint32_t unit_tx = kKBytes + kHalf * Rv;
+    const bool slot_axis1 = ta.slot_axis == 1;
+    int hk_of[kG];
 #pragma unroll
-    for (int k = 0; k < kKPerLane; ++k) {
-      const int s = lo + r0 + 8 * k;
-      slot_nxt[k] = -1;
-      if (s < hi) slot_nxt[k] = page[s];
-    }
+    for (int g = 0; g < kG; ++g) hk_of[g] = (h0 + min(g, G - 1)) / gqa;
+
+    // page-table entries of rows 4*lane .. 4*lane+3 of a tile, fetched one tile ahead
+    auto load4 = [&](int t, int (&e)[4]) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int s = lo + t * kTile + 4 * lane + j;
+        e[j] = -1;
+        if (s < hi) e[j] = page[s];
+      }
+    };
+    int e_cur[4], e_nxt[4];
+    load4(0, e_nxt);
     bool ok = true;
-    int u = 0;
+    int slot_j = 0;            // slot (within each head's ring) of the next half-tile
+    uint32_t wait_parity = 1;  // parity of the ring's previous lap: passes at once on the first lap
     for (int t = 0; t < ntiles && ok; ++t) {
       if (pw == 0) WSVD_TRACE(0, t, 0);
 #pragma unroll
-      for (int k = 0; k < kKPerLane; ++k) slot_cur[k] = slot_nxt[k];
-      if (t + 1 < ntiles) {
+      for (int j = 0; j < 4; ++j) e_cur[j] = e_nxt[j];
+      if (t + 1 < ntiles) load4(t + 1, e_nxt);
+      // TMA needs the tile's token slots to be consecutive (an affine page table)
+      const int first_slot = __shfl_sync(0xffffffffu, e_cur[0], 0);
+      bool affine = true;
 #pragma unroll
-        for (int k = 0; k < kKPerLane; ++k) {
-          const int s = lo + (t + 1) * kTile + r0 + 8 * k;
-          slot_nxt[k] = -1;
-          if (s < hi) slot_nxt[k] = page[s];
-        }
-      }
-      const bool full_tile = lo + (t + 1) * kTile <= hi;
-      for (int g = 0; g < G; ++g, ++u) {
-        const int stage = u % kStages;
-        if (pw == 0) WSVD_TRACE(6, u, 0);
-        if (u >= kStages && !mbar_wait(bar_empty(stage), ((u / kStages) - 1) & 1)) {
-          atomicMax(&g_status, (unsigned)kTimeoutProducer);
-          ok = false;
-          break;
-        }
-        if (pw == 0) WSVD_TRACE(6, u, 1);
-        const uint8_t* src = base + (int64_t)((h0 + g) / gqa) * hstride;
-        const uint32_t dst = sRing + stage * kUnitBytes + doff;
-        if (chunk_on) {
-          if (full_tile) {
-#pragma unroll
-            for (int k = 0; k < kKPerLane; ++k) cp_async16(dst + k * 512, src + (int64_t)slot_cur[k] * tstride, 16u);
-          } else {
-#pragma unroll
-            for (int k = 0; k < kKPerLane; ++k) {
-              const bool valid = slot_cur[k] >= 0;  // rows past the end are zero-filled
-              cp_async16(dst + k * 512, src + (int64_t)(valid ? slot_cur[k] : 0) * tstride, valid ? 16u : 0u);
+      for (int j = 0; j < 4; ++j) affine = affine && (e_cur[j] < 0 || e_cur[j] == first_slot + 4 * lane + j);
+      const bool tile_tma = ta.use_tma && __all_sync(0xffffffffu, affine);
+      for (int half = 0; half < 2 && ok; ++half) {
+        if (tile_tma) {
+          for (int g = 0; g < G; ++g) {
+            const int stage = g * kSlots + slot_j;
+            if (!mbar_wait(bar_empty(stage), wait_parity)) {
+              ok = false;
+              break;
+            }
+            // two TMA copies of 64 consecutive token slots; lane 0's expect_tx is its arrival
+            if (lane == 0) {
+              const int sl = first_slot + half * kHalf;
+              const int c1 = slot_axis1 ? sl : hk_of[g], c2 = slot_axis1 ? hk_of[g] : sl;
+              mbar_expect_tx(bar_full(stage), unit_tx);
+              tma_load_3d(sRing + stage * kUnitBytes, &ta.tmap_k, 0, c1, c2, bar_full(stage));
+              tma_load_3d(sRing + stage * kUnitBytes + kKBytes, &ta.tmap_v, 0, c1, c2, bar_full(stage));
+            } else {
+              mbar_arrive(bar_full(stage));
             }
           }
+        } else {
+          // Gather: lane (r0 = lane/4, c = lane%4) copies 16-byte chunk c of rows r0 + 8k of
+          // the half-tile.  K chunks are XOR-swizzled with (row/2)%4 exactly as the TMA
+          // 64-byte swizzle places them; (row/2)%4 does not depend on k.
+          const int c = lane & 3, r0 = lane >> 2;
+          const uint32_t doff_k = r0 * 64 + ((c ^ ((r0 >> 1) & 3)) << 4);
+          const uint32_t doff_v = kKBytes + r0 * Rv + c * 16;
+          const bool v_on = c < (Rv >> 4);
+          int32_t slot[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int s = lo + t * kTile + half * kHalf + r0 + 8 * k;
+            slot[k] = -1;
+            if (s < hi) slot[k] = page[s];
+          }
+          for (int g = 0; g < G; ++g) {
+            const int stage = g * kSlots + slot_j;
+            if (!mbar_wait(bar_empty(stage), wait_parity)) {
+              ok = false;
+              break;
+            }
+            const uint8_t* ksrc = kbase + c * 16 + (int64_t)hk_of[g] * p.k_stride_h;
+            const uint8_t* vsrc = vbase_g + c * 16 + (int64_t)hk_of[g] * p.v_stride_h;
+            const uint32_t dst = sRing + stage * kUnitBytes;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const bool valid = slot[k] >= 0;  // rows past the end are zero-filled
+              const int64_t sl = valid ? slot[k] : 0;
+              cp_async16(dst + doff_k + k * 512, ksrc + sl * kst, valid ? 16u : 0u);
+              if (v_on) cp_async16(dst + doff_v + k * 8 * Rv, vsrc + sl * vst, valid ? 16u : 0u);
+            }
+            cp_async_arrive_noinc(bar_full(stage));
+          }
         }
-        if (pw == 0) WSVD_TRACE(6, u, 3);
-        cp_async_arrive_noinc(bar_full(stage));
-        if (pw == 0) WSVD_TRACE(6, u, 2);
-      }
-      // Ask for the rows of tile t + kPrefetchTiles to be brought into L2 (one bulk
-      // prefetch per head when the 128 rows are contiguous in memory) so that the ring
-      // only has to cover the L2 -> shared-memory latency, not the DRAM latency.
-      if (kPrefetchTiles > 0 && pw < 2 && lane == 0 && t + kPrefetchTiles < ntiles) {
-        const int s0 = lo + (t + kPrefetchTiles) * kTile;
-        const int rows = min(kTile, hi - s0);
-        const int rowbytes = is_v ? Rv : kRk;
-        if (tstride == rowbytes && page[s0 + rows - 1] - page[s0] == rows - 1) {
-          const int64_t sl0 = page[s0];
-          for (int g = 0; g < G; ++g)
-            prefetch_l2_bulk(base - c * 16 + (int64_t)((h0 + g) / gqa) * hstride + sl0 * tstride, rows * rowbytes);
+        if (++slot_j == kSlots) {
+          slot_j = 0;
+          wait_parity ^= 1;
         }
       }
       if (pw == 0) WSVD_TRACE(0, t, 1);
     }
+    if (!ok) atomicMax(&g_status, (unsigned)kTimeoutProducer);
     cp_async_wait_all();
   } else if (warp == kMmaWarp) {
     // ================================================================= table loads + MMA issue
@@ -412,10 +454,19 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       };
       issue_table(0);
       if (ntiles > 1) issue_table(1);
+      // descriptors: only the start-address field changes between k-steps and buffers
+      const uint64_t adesc0 = smem_desc_sw128(sA), bdesc0 = smem_desc_sw128(sB);
       bool ok = mbar_wait(bar_pq, 0);
       for (int t = 0; t < ntiles && ok; ++t) {
         const int buf = t & 1;
         WSVD_TRACE(1, t, 0);
+        // The table tile of t+1 goes into the buffer MMA(t-1) read; that MMA was issued a
+        // whole iteration ago, so this wait is short and the load overlaps MMA(t).
+        if (t >= 1 && t + 1 < ntiles) {
+          ok = mbar_wait(bar_a_empty((t + 1) & 1), ((t - 1) >> 1) & 1);
+          if (!ok) break;
+          issue_table(t + 1);
+        }
         ok = mbar_wait(bar_a_full(buf), (t >> 1) & 1);
         WSVD_TRACE(1, t, 1);
         if (ok && t >= 2) ok = mbar_wait(bar_w_empty(buf), ((t >> 1) - 1) & 1);
@@ -426,18 +477,13 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t koff = (kk & 3) * 32;
-          const uint64_t ad = smem_desc_sw128(sA + buf * kABufBytes + (kk >> 2) * kAHalfBytes + koff);
-          const uint64_t bd = smem_desc_sw128(sB + (kk >> 2) * kBHalfBytes + koff);
+          const uint64_t ad = adesc0 + ((buf * kABufBytes + (kk >> 2) * kAHalfBytes + koff) >> 4);
+          const uint64_t bd = bdesc0 + (((kk >> 2) * kBHalfBytes + koff) >> 4);
           umma_f16(d_tmem, ad, bd, idesc, kk > 0);
         }
         umma_commit(bar_w_full(buf));
         umma_commit(bar_a_empty(buf));
         WSVD_TRACE(1, t, 3);
-        if (t + 1 < ntiles && t + 1 >= 2) {
-          ok = mbar_wait(bar_a_empty((t + 1) & 1), (((t + 1) >> 1) - 1) & 1);
-          if (ok) issue_table(t + 1);
-        }
-        WSVD_TRACE(1, t, 4);
       }
       if (!ok) atomicMax(&g_status, (unsigned)kTimeoutMma);
     }
@@ -537,33 +583,53 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
     uint64_t acc[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) acc[e] = 0ull;
+    const int rg = lane & 3, tg = lane >> 2;
+    const bool pv_on = rg < (Rv >> 4);
     unsigned short sk_raw, sv_raw, sk_n = 0, sv_n = 0;
+    uint4 v_cur[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v_cur[k] = make_uint4(0u, 0u, 0u, 0u);
     int slot_n;
     load_slot(lo + row, slot_n);
     load_scales(slot_n, sk_raw, sv_raw);
     load_slot(lo + kTile + row, slot_n);
-    const int rg = lane & 3, tg = lane >> 2;
-    const bool pv_on = rg < (Rv >> 4);
     bool ok = true;
 
     for (int t = 0; t < ntiles; ++t) {
       const int s = lo + t * kTile + row;
       const bool valid = s < hi;
-      const int u = t * G + g, stage = u % kStages, buf = t & 1;
+      // this warp's 32 tokens lie in half-tile q4/2 of the tile: the head's nth half-tile
+      const int nth = 2 * t + (q4 >> 1), nth_other = 2 * t + 1 - (q4 >> 1);
+      const int stage = g * kSlots + nth % kSlots, buf = t & 1;
       if (q4 == 0) WSVD_TRACE(2 + g, t, 0);
       load_scales(slot_n, sk_n, sv_n);
       load_slot(s + 2 * kTile, slot_n);
       if (q4 == 0) WSVD_TRACE(2 + g, t, 1);
-      ok = mbar_wait(bar_full(stage), (u / kStages) & 1);
+      // Also observe the tile's other half-tile: a slot alternates between the two warp
+      // pairs of the head, and a parity wait is only sound if the waiter has seen the
+      // slot's previous phase complete (copies may land out of order).
+      ok = mbar_wait(bar_full(stage), (nth / kSlots) & 1) &&
+           mbar_wait(bar_full(g * kSlots + nth_other % kSlots), (nth_other / kSlots) & 1);
       if (q4 == 0) WSVD_TRACE(2 + g, t, 2);
       ok = ok && mbar_wait(bar_w_full(buf), (t >> 1) & 1);
       if (q4 == 0) WSVD_TRACE(2 + g, t, 3);
       if (!ok) break;
       tc_fence_after();
 
+      // ---- V rows of this warp's 32 tokens into registers (lane (rg, tg): chunk rg of rows
+      //      tg + 8k), so that the ring slot can be handed back right after the score
+      if (pv_on) {
+        const uint32_t vsm = sRing + stage * kUnitBytes + kKBytes + ((q4 & 1) * 32 + tg) * Rv + rg * 16;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(v_cur[k].x), "=r"(v_cur[k].y), "=r"(v_cur[k].z), "=r"(v_cur[k].w)
+                       : "r"(vsm + k * 8 * Rv));
+      }
+
       // ---- score: dot of this token's int8 K row with its row of W, in two halves of 32
       //      ranks, four independent accumulators
-      const uint32_t krow = sRing + stage * kUnitBytes + row * 64;
+      const uint32_t krow = sRing + stage * kUnitBytes + (row & (kHalf - 1)) * 64;
       const uint32_t sw = (row >> 1) & 3;
       const uint32_t taddr = tmem + ((uint32_t)(q4 * 32) << 16) + buf * (kG * kRk) + g * kRk;
       uint64_t dot[4] = {0ull, 0ull, 0ull, 0ull};
@@ -597,7 +663,10 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       const uint64_t dot2 = add2(add2(dot[0], dot[1]), add2(dot[2], dot[3]));
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_w_empty(buf));
+      if (lane == 0) {
+        mbar_arrive(bar_w_empty(buf));   // this warp has read its rows of W ...
+        mbar_arrive(bar_empty(stage));   // ... and its K rows: both buffers can be refilled
+      }
       if (q4 == 0) WSVD_TRACE(2 + g, t, 4);
       float d0, d1;
       upk(dot2, d0, d1);
@@ -620,30 +689,20 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       if (q4 == 0) WSVD_TRACE(2 + g, t, 5);
 
       // ---- P.V on the CUDA cores: this lane owns 16 ranks (chunk rg) of tokens tg + 8k
-      const uint32_t vbase = sRing + stage * kUnitBytes + kKBytes + (q4 * 32) * 64;
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const int j = tg + 8 * k;
-        const float pj = __shfl_sync(0xffffffffu, pvs, j);
-        if (pv_on) {
-          const int vr = q4 * 32 + j;
-          uint4 vw;
-          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                       : "=r"(vw.x), "=r"(vw.y), "=r"(vw.z), "=r"(vw.w)
-                       : "r"(vbase + j * 64 + ((rg ^ ((vr >> 1) & 3)) << 4)));
-          const uint32_t vws[4] = {vw.x ^ 0x80808080u, vw.y ^ 0x80808080u, vw.z ^ 0x80808080u, vw.w ^ 0x80808080u};
-          const uint64_t pj2 = pk(pj, pj);
+        const float pj = __shfl_sync(0xffffffffu, pvs, tg + 8 * k);
+        const uint32_t vws[4] = {v_cur[k].x ^ 0x80808080u, v_cur[k].y ^ 0x80808080u, v_cur[k].z ^ 0x80808080u,
+                                 v_cur[k].w ^ 0x80808080u};
+        const uint64_t pj2 = pk(pj, pj);
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj) {
-            uint64_t x01, x23;
-            cvt4(vws[jj], x01, x23);
-            acc[2 * jj] = fma2(x01, pj2, acc[2 * jj]);
-            acc[2 * jj + 1] = fma2(x23, pj2, acc[2 * jj + 1]);
-          }
+        for (int jj = 0; jj < 4; ++jj) {
+          uint64_t x01, x23;
+          cvt4(vws[jj], x01, x23);
+          acc[2 * jj] = fma2(x01, pj2, acc[2 * jj]);
+          acc[2 * jj + 1] = fma2(x23, pj2, acc[2 * jj + 1]);
         }
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_empty(stage));
       if (q4 == 0) WSVD_TRACE(2 + g, t, 6);
       sk_raw = sk_n;
       sv_raw = sv_n;
@@ -705,6 +764,65 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
 
 }  // namespace tc
 
+namespace tc {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      ptr = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+// One latent tensor [T, Hkv, R] int8 with byte strides (st, sh) as a 3-D tensor map whose
+// outer axes are ordered by stride; box = 64 token slots x 1 head x R bytes.
+bool encode_one(CUtensorMap* map, const void* base, int64_t st, int64_t sh, int64_t T, int Hkv, int R,
+                CUtensorMapSwizzle swz, int* slot_axis) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn || T <= 0 || T > 0xffffffffll) return false;
+  const bool slot_first = st <= sh;  // head-major storage: the slot axis has the smaller stride
+  cuuint64_t dims[3] = {(cuuint64_t)R, (cuuint64_t)(slot_first ? T : Hkv), (cuuint64_t)(slot_first ? Hkv : T)};
+  cuuint64_t strides[2] = {(cuuint64_t)(slot_first ? st : sh), (cuuint64_t)(slot_first ? sh : st)};
+  cuuint32_t box[3] = {(cuuint32_t)R, (cuuint32_t)(slot_first ? kHalf : 1), (cuuint32_t)(slot_first ? 1 : kHalf)};
+  cuuint32_t estr[3] = {1, 1, 1};
+  *slot_axis = slot_first ? 1 : 2;
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+void encode_latent_maps(const WsvdLatentDecodeParams& p, TcArgs* ta) {
+  ta->use_tma = 0;
+  ta->slot_axis = 1;
+  memset(&ta->tmap_k, 0, sizeof(CUtensorMap));
+  memset(&ta->tmap_v, 0, sizeof(CUtensorMap));
+#ifdef WSVD_TC_NO_TMA
+  return;
+#endif
+  if (p.n_token_slots <= 0) return;
+  int ax_k = 1;
+  if (!encode_one(&ta->tmap_k, p.latent_k, p.k_stride_t, p.k_stride_h, p.n_token_slots, p.n_kv_heads, kRk,
+                  CU_TENSOR_MAP_SWIZZLE_64B, &ax_k))
+    return;
+  int ax_v = 1;
+  if (!encode_one(&ta->tmap_v, p.latent_v, p.v_stride_t, p.v_stride_h, p.n_token_slots, p.n_kv_heads, p.rank_v,
+                  CU_TENSOR_MAP_SWIZZLE_NONE, &ax_v) || ax_v != ax_k)
+    return;
+  ta->slot_axis = ax_k;
+  ta->use_tma = 1;
+}
+
+}  // namespace tc
+
 size_t rope_table_bytes(int rows) { return (size_t)rows * 256; }
 
 cudaError_t launch_rope_table(void* table, int rows, const KArgs& a, cudaStream_t stream) {
@@ -722,6 +840,7 @@ cudaError_t launch_stage1_tc(const KArgs& a, const void* table, int table_rows, 
   ta.k = a;
   ta.table = reinterpret_cast<const uint8_t*>(table);
   ta.table_rows = table_rows;
+  tc::encode_latent_maps(a.p, &ta);
   dim3 grid(a.n_splits, (a.p.n_q_heads + tc::kG - 1) / tc::kG, a.p.batch);
   tc::stage1_tc_kernel<<<grid, tc::kThreads, tc::kSmemBytes, stream>>>(ta);
   return cudaGetLastError();

@@ -146,6 +146,7 @@ def build_params(
     p.split_len = int(split_len)
     p.kernel = KERNEL[kernel]
     p.theta, p.sm_scale = float(theta), float(sm_scale)
+    p.n_token_slots = min(latent_k.shape[0], latent_v.shape[0])
     if D == 128 and kernel != "generic":
         table, rows = rope_table(q.device, int(max_len), D, theta)
         p.rope_table, p.rope_table_rows = table.data_ptr(), rows
