@@ -40,10 +40,8 @@ constexpr int kG = 4;          // heads per CTA
 constexpr int kTile = 128;     // positions per MMA tile (= tensor-memory lanes)
 constexpr int kRk = 64;
 constexpr int kEpiWarps = 4 * kG;
-constexpr int kProducerWarps = 1;
-constexpr int kProducerWarp0 = kEpiWarps;
-constexpr int kMmaWarp = kEpiWarps + kProducerWarps;
-constexpr int kThreads = (kEpiWarps + kProducerWarps + 1) * 32;
+constexpr int kMmaWarp = kEpiWarps;
+constexpr int kThreads = (kEpiWarps + 1) * 32;
 // Latent ring: every head owns kSlots slots, each holding half a tile (64 tokens): K rows
 // at a 64-byte pitch followed by V rows at a rank_v pitch.  A slot is only ever reused by
 // the same head, whose warps consume their slots in order; with slots shared between heads
@@ -68,7 +66,8 @@ constexpr uint32_t kOffQ = kOffRing + kStages * kUnitBytes;
 constexpr uint32_t kOffBar = kOffQ + kG * 128 * 4;
 constexpr int kNumBars = 2 * kStages + 2 + 2 + 2 + 2 + 1;
 constexpr uint32_t kOffTmemSlot = kOffBar + kNumBars * 8;
-constexpr uint32_t kSmemBytes = kOffTmemSlot + 16;  // the dynamic shared-memory base is 1024-byte aligned
+constexpr uint32_t kOffIssued = kOffTmemSlot + 16;   // per ring slot: number of units requested so far
+constexpr uint32_t kSmemBytes = kOffIssued + kStages * 4;  // the dynamic shared-memory base is 1024-byte aligned
 
 enum Status : unsigned int { kOk = 0, kTimeoutProducer = 1, kTimeoutMma = 2, kTimeoutEpilogue = 3, kBadSmemAlignment = 4 };
 
@@ -306,11 +305,16 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
 
   const int32_t* page = p.req_to_token + (int64_t)p.b_req_idx[b] * p.rtt_stride;
 
-  // ---- set-up: barriers + tensor memory (warp 17), scaled q to shared memory (epilogue warps)
+  // 16-byte vector loads of wk need f16 data with 16-byte aligned rows
+  const bool wk_vec = p.wk_dtype == WSVD_F16 && (p.wk_stride_r & 7) == 0 &&
+                      (reinterpret_cast<uintptr_t>(p.wk) & 15) == 0;
+  uint4 wpre[8];
+
+  // ---- set-up: barriers + tensor memory (MMA warp), scaled q to shared memory (epilogue warps)
   if (warp == kMmaWarp) {
     if (lane == 0) {
       for (int s = 0; s < kStages; ++s) {
-        mbar_init(bar_full(s), 32 * kProducerWarps);   // one asynchronous arrive per producer lane
+        mbar_init(bar_full(s), 32);   // one arrive per lane of the warp that issues the copy
         mbar_init(bar_empty(s), 2);   // the two epilogue warps that own the half-tile's tokens
       }
       for (int i = 0; i < 2; ++i) {
@@ -320,6 +324,7 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
         mbar_init(bar_w_empty(i), 4 * G);
       }
       mbar_init(bar_pq, 4 * G);
+      for (int i = 0; i < kStages; ++i) reinterpret_cast<volatile int*>(sm + kOffIssued)[i] = 0;
       fence_barrier_init();
     }
     __syncwarp();
@@ -327,6 +332,18 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
     tmem_relinquish();
     tc_fence_before();
   } else if (warp < 4 * G) {
+    // the head's slice of wk for the [P;Q] build: requested now, used after the barrier
+    if (wk_vec) {
+      const int hk_pre = (h0 + (warp >> 2)) / gqa;
+      const bool il = p.rope_layout == WSVD_ROPE_INTERLEAVED;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int task = (threadIdx.x & 127) + 128 * i, r = task >> 3, ic = task & 7;
+        const __half* w = reinterpret_cast<const __half*>(p.wk) + (int64_t)r * p.wk_stride_r + (int64_t)hk_pre * 128;
+        wpre[2 * i] = *reinterpret_cast<const uint4*>(w + (il ? ic * 16 : ic * 8));
+        wpre[2 * i + 1] = *reinterpret_cast<const uint4*>(w + (il ? ic * 16 + 8 : 64 + ic * 8));
+      }
+    }
     // q * sm_scale * log2(e): scores come out in the log2 domain
     const float qscale = a.sm_scale * 1.4426950408889634f;
     for (int idx = threadIdx.x; idx < G * 128; idx += 128 * G) {
@@ -340,107 +357,7 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
   const uint32_t tmem = *tmem_slot;
   if (warp == 0) WSVD_TRACE(7, 0, 1);
 
-  if (warp >= kProducerWarp0 && warp < kProducerWarp0 + kProducerWarps) {
-    // ================================================================= producers
-    // One warp fills every head's slots, half-tile by half-tile, in order.
-    const int pw = warp - kProducerWarp0;
-    const uint8_t* kbase = reinterpret_cast<const uint8_t*>(p.latent_k);
-    const uint8_t* vbase_g = reinterpret_cast<const uint8_t*>(p.latent_v);
-    const int kst = (int)p.k_stride_t, vst = (int)p.v_stride_t;
-    const uint32_t unit_tx = kKBytes + kHalf * Rv;
-    const bool slot_axis1 = ta.slot_axis == 1;
-    int hk_of[kG];
-#pragma unroll
-    for (int g = 0; g < kG; ++g) hk_of[g] = (h0 + min(g, G - 1)) / gqa;
-
-    // page-table entries of rows 4*lane .. 4*lane+3 of a tile, fetched one tile ahead
-    auto load4 = [&](int t, int (&e)[4]) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int s = lo + t * kTile + 4 * lane + j;
-        e[j] = -1;
-        if (s < hi) e[j] = page[s];
-      }
-    };
-    int e_cur[4], e_nxt[4];
-    load4(0, e_nxt);
-    bool ok = true;
-    int slot_j = 0;            // slot (within each head's ring) of the next half-tile
-    uint32_t wait_parity = 1;  // parity of the ring's previous lap: passes at once on the first lap
-    for (int t = 0; t < ntiles && ok; ++t) {
-      if (pw == 0) WSVD_TRACE(0, t, 0);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) e_cur[j] = e_nxt[j];
-      if (t + 1 < ntiles) load4(t + 1, e_nxt);
-      // TMA needs the tile's token slots to be consecutive (an affine page table)
-      const int first_slot = __shfl_sync(0xffffffffu, e_cur[0], 0);
-      bool affine = true;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) affine = affine && (e_cur[j] < 0 || e_cur[j] == first_slot + 4 * lane + j);
-      const bool tile_tma = ta.use_tma && __all_sync(0xffffffffu, affine);
-      for (int half = 0; half < 2 && ok; ++half) {
-        if (tile_tma) {
-          for (int g = 0; g < G; ++g) {
-            const int stage = g * kSlots + slot_j;
-            if (!mbar_wait(bar_empty(stage), wait_parity)) {
-              ok = false;
-              break;
-            }
-            // two TMA copies of 64 consecutive token slots; lane 0's expect_tx is its arrival
-            if (lane == 0) {
-              const int sl = first_slot + half * kHalf;
-              const int c1 = slot_axis1 ? sl : hk_of[g], c2 = slot_axis1 ? hk_of[g] : sl;
-              mbar_expect_tx(bar_full(stage), unit_tx);
-              tma_load_3d(sRing + stage * kUnitBytes, &ta.tmap_k, 0, c1, c2, bar_full(stage));
-              tma_load_3d(sRing + stage * kUnitBytes + kKBytes, &ta.tmap_v, 0, c1, c2, bar_full(stage));
-            } else {
-              mbar_arrive(bar_full(stage));
-            }
-          }
-        } else {
-          // Gather: lane (r0 = lane/4, c = lane%4) copies 16-byte chunk c of rows r0 + 8k of
-          // the half-tile.  K chunks are XOR-swizzled with (row/2)%4 exactly as the TMA
-          // 64-byte swizzle places them; (row/2)%4 does not depend on k.
-          const int c = lane & 3, r0 = lane >> 2;
-          const uint32_t doff_k = r0 * 64 + ((c ^ ((r0 >> 1) & 3)) << 4);
-          const uint32_t doff_v = kKBytes + r0 * Rv + c * 16;
-          const bool v_on = c < (Rv >> 4);
-          int32_t slot[8];
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const int s = lo + t * kTile + half * kHalf + r0 + 8 * k;
-            slot[k] = -1;
-            if (s < hi) slot[k] = page[s];
-          }
-          for (int g = 0; g < G; ++g) {
-            const int stage = g * kSlots + slot_j;
-            if (!mbar_wait(bar_empty(stage), wait_parity)) {
-              ok = false;
-              break;
-            }
-            const uint8_t* ksrc = kbase + c * 16 + (int64_t)hk_of[g] * p.k_stride_h;
-            const uint8_t* vsrc = vbase_g + c * 16 + (int64_t)hk_of[g] * p.v_stride_h;
-            const uint32_t dst = sRing + stage * kUnitBytes;
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              const bool valid = slot[k] >= 0;  // rows past the end are zero-filled
-              const int64_t sl = valid ? slot[k] : 0;
-              cp_async16(dst + doff_k + k * 512, ksrc + sl * kst, valid ? 16u : 0u);
-              if (v_on) cp_async16(dst + doff_v + k * 8 * Rv, vsrc + sl * vst, valid ? 16u : 0u);
-            }
-            cp_async_arrive_noinc(bar_full(stage));
-          }
-        }
-        if (++slot_j == kSlots) {
-          slot_j = 0;
-          wait_parity ^= 1;
-        }
-      }
-      if (pw == 0) WSVD_TRACE(0, t, 1);
-    }
-    if (!ok) atomicMax(&g_status, (unsigned)kTimeoutProducer);
-    cp_async_wait_all();
-  } else if (warp == kMmaWarp) {
+  if (warp == kMmaWarp) {
     // ================================================================= table loads + MMA issue
     if (lane == 0) {
       const uint32_t idesc = instr_desc_f16(kTile, kRk * G);
@@ -495,22 +412,98 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
     const int row = q4 * 32 + lane;
     const bool interleaved = p.rope_layout == WSVD_ROPE_INTERLEAVED;
 
+    // ---- latent copies.  The head's half-tiles (units n = 2*tile + half) cycle through
+    //      its kSlots ring slots.  Unit n is requested by the first warp of the pair that
+    //      consumed unit n - kSlots, as soon as that pair has handed the slot back, so every
+    //      head streams independently of the others.
+    const uint8_t* kbase = reinterpret_cast<const uint8_t*>(p.latent_k) + (int64_t)hk * p.k_stride_h;
+    const uint8_t* vbase_g = reinterpret_cast<const uint8_t*>(p.latent_v) + (int64_t)hk * p.v_stride_h;
+    const uint32_t unit_tx = kKBytes + kHalf * Rv;
+    const int n_units = 2 * ntiles;
+    // page entries of the unit's 64 rows (two per lane) and of its tile's first row
+    auto fetch_entries = [&](int n, int& e0, int& e1, int& first) {
+      const int s0t = lo + (n >> 1) * kTile, sa = s0t + (n & 1) * kHalf + 2 * lane;
+      e0 = -1;
+      e1 = -1;
+      if (sa < hi) e0 = page[sa];
+      if (sa + 1 < hi) e1 = page[sa + 1];
+      first = page[s0t];
+    };
+    auto issue_unit = [&](int n, int e0, int e1, int first) {
+      const int stage = g * kSlots + n % kSlots;
+      const int sl0 = first + (n & 1) * kHalf;  // slot of the unit's first row if the tile is affine
+      const bool affine = (e0 < 0 || e0 == sl0 + 2 * lane) && (e1 < 0 || e1 == sl0 + 2 * lane + 1);
+      if (ta.use_tma && __all_sync(0xffffffffu, affine)) {
+        // two TMA copies of 64 consecutive token slots; lane 0's expect_tx is its arrival
+        if (lane == 0) {
+          const int c1 = ta.slot_axis == 1 ? sl0 : hk, c2 = ta.slot_axis == 1 ? hk : sl0;
+          mbar_expect_tx(bar_full(stage), unit_tx);
+          tma_load_3d(sRing + stage * kUnitBytes, &ta.tmap_k, 0, c1, c2, bar_full(stage));
+          tma_load_3d(sRing + stage * kUnitBytes + kKBytes, &ta.tmap_v, 0, c1, c2, bar_full(stage));
+        } else {
+          mbar_arrive(bar_full(stage));
+        }
+      } else {
+        // Gather through the page table: lane (r0 = lane/4, c = lane%4) copies 16-byte chunk
+        // c of rows r0 + 8k.  K chunks are XOR-swizzled with (row/2)%4 exactly as the TMA
+        // 64-byte swizzle places them; (row/2)%4 does not depend on k.
+        const int c = lane & 3, r0 = lane >> 2;
+        const uint32_t dst = sRing + stage * kUnitBytes;
+        const uint32_t doff_k = r0 * 64 + ((c ^ ((r0 >> 1) & 3)) << 4);
+        const uint32_t doff_v = kKBytes + r0 * Rv + c * 16;
+        const bool v_on = c < (Rv >> 4);
+        const int s0 = lo + (n >> 1) * kTile + (n & 1) * kHalf + r0;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const bool valid = s0 + 8 * k < hi;  // rows past the end are zero-filled
+          const int64_t sl = valid ? page[s0 + 8 * k] : 0;
+          cp_async16(dst + doff_k + k * 512, kbase + c * 16 + sl * p.k_stride_t, valid ? 16u : 0u);
+          if (v_on) cp_async16(dst + doff_v + k * 8 * Rv, vbase_g + c * 16 + sl * p.v_stride_t, valid ? 16u : 0u);
+        }
+        cp_async_arrive_noinc(bar_full(stage));
+      }
+      // Publish "unit n has been requested".  A consumer waits for this before it waits on
+      // the slot's mbarrier: the request is made only after the slot's previous unit was
+      // consumed, so from then on the parity wait cannot be a phase ahead or behind.
+      __syncwarp();
+      if (lane == 0)
+        asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(sbase + kOffIssued + 4u * stage), "r"(n / kSlots + 1)
+                     : "memory");
+    };
+    auto wait_issued = [&](int stage, int uses) -> bool {
+      const uint32_t addr = sbase + kOffIssued + 4u * stage;
+      const uint64_t t0 = global_ns();
+      for (;;) {
+        uint32_t v;
+        asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+        if ((int)v >= uses) return true;
+        if (global_ns() - t0 > 2000000000ull) return false;
+      }
+    };
+    const bool issuer = (q4 & 1) == 0;  // warps 0 and 2 of the head request the copies
+    if (issuer) {
+      // the first kSlots units, so that the stream starts while [P;Q] is being built
+      for (int n = q4 >> 1; n < kSlots && n < n_units; n += 2) {
+        int e0, e1, first;
+        fetch_entries(n, e0, e1, first);
+        issue_unit(n, e0, e1, first);
+      }
+    }
+
     // ---- B operand: P (cos coefficients) and Q (sin coefficients) of this head, f16,
     //      rows n = g*64 + r, 64 frequencies per row, 128-byte swizzle
     {
       const float* qg = qs + g * 128;
       const int tid = threadIdx.x & 127;
       const int64_t col = (int64_t)hk * 128;
-      const bool vec = p.wk_dtype == WSVD_F16 && (p.wk_stride_r & 7) == 0 &&
-                       (reinterpret_cast<uintptr_t>(p.wk) & 15) == 0;
-      for (int task = tid; task < 64 * 8; task += 128) {
+#pragma unroll
+      for (int it = 0; it < 4; ++it) {
+        const int task = tid + 128 * it;
         const int r = task >> 3, ic = task & 7;  // rank, chunk of 8 frequencies
         float u0[8], u1[8];
-        if (vec) {
+        if (wk_vec) {
           // half layout: dims ic*8.. and 64+ic*8..; interleaved: 16 consecutive dims
-          const __half* w = reinterpret_cast<const __half*>(p.wk) + (int64_t)r * p.wk_stride_r + col;
-          const uint4 a0 = *reinterpret_cast<const uint4*>(w + (interleaved ? ic * 16 : ic * 8));
-          const uint4 a1 = *reinterpret_cast<const uint4*>(w + (interleaved ? ic * 16 + 8 : 64 + ic * 8));
+          const uint4 a0 = wpre[2 * it], a1 = wpre[2 * it + 1];
           const __half* h0p = reinterpret_cast<const __half*>(&a0);
           const __half* h1p = reinterpret_cast<const __half*>(&a1);
 #pragma unroll
@@ -599,17 +592,16 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       const int s = lo + t * kTile + row;
       const bool valid = s < hi;
       // this warp's 32 tokens lie in half-tile q4/2 of the tile: the head's nth half-tile
-      const int nth = 2 * t + (q4 >> 1), nth_other = 2 * t + 1 - (q4 >> 1);
+      const int nth = 2 * t + (q4 >> 1);
       const int stage = g * kSlots + nth % kSlots, buf = t & 1;
       if (q4 == 0) WSVD_TRACE(2 + g, t, 0);
       load_scales(slot_n, sk_n, sv_n);
       load_slot(s + 2 * kTile, slot_n);
+      const int n_issue = nth + kSlots;  // the unit that will reuse this warp's slot
+      int ie0 = -1, ie1 = -1, ifirst = 0;
+      if (issuer && n_issue < n_units) fetch_entries(n_issue, ie0, ie1, ifirst);
       if (q4 == 0) WSVD_TRACE(2 + g, t, 1);
-      // Also observe the tile's other half-tile: a slot alternates between the two warp
-      // pairs of the head, and a parity wait is only sound if the waiter has seen the
-      // slot's previous phase complete (copies may land out of order).
-      ok = mbar_wait(bar_full(stage), (nth / kSlots) & 1) &&
-           mbar_wait(bar_full(g * kSlots + nth_other % kSlots), (nth_other / kSlots) & 1);
+      ok = wait_issued(stage, nth / kSlots + 1) && mbar_wait(bar_full(stage), (nth / kSlots) & 1);
       if (q4 == 0) WSVD_TRACE(2 + g, t, 2);
       ok = ok && mbar_wait(bar_w_full(buf), (t >> 1) & 1);
       if (q4 == 0) WSVD_TRACE(2 + g, t, 3);
@@ -665,7 +657,15 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(bar_w_empty(buf));   // this warp has read its rows of W ...
-        mbar_arrive(bar_empty(stage));   // ... and its K rows: both buffers can be refilled
+        mbar_arrive(bar_empty(stage));   // ... and its K and V rows
+      }
+      if (issuer && n_issue < n_units) {
+        // once the pair's other warp has let go of the slot too, refill it
+        if (!mbar_wait(bar_empty(stage), (nth / kSlots) & 1)) {
+          ok = false;
+          break;
+        }
+        issue_unit(n_issue, ie0, ie1, ifirst);
       }
       if (q4 == 0) WSVD_TRACE(2 + g, t, 4);
       float d0, d1;
