@@ -309,6 +309,7 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
   const bool wk_vec = p.wk_dtype == WSVD_F16 && (p.wk_stride_r & 7) == 0 &&
                       (reinterpret_cast<uintptr_t>(p.wk) & 15) == 0;
   uint4 wpre[8];
+  int pre_e[6] = {-1, -1, 0, -1, -1, 0};
 
   // ---- set-up: barriers + tensor memory (MMA warp), scaled q to shared memory (epilogue warps)
   if (warp == kMmaWarp) {
@@ -332,6 +333,26 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
     tmem_relinquish();
     tc_fence_before();
   } else if (warp < 4 * G) {
+    if (ta.use_tma && warp == 0 && lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&ta.tmap_k)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&ta.tmap_v)) : "memory");
+    }
+    // page entries of the first ring units (requested now, used after the barrier)
+    if ((warp & 1) == 0) {
+      const int nq = (warp & 3) >> 1;  // issuing warp 0 of the head starts units 0 and 2, warp 2 unit 1
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int n = nq + 2 * i;
+        if (n < kSlots && n < 2 * ntiles) {
+          const int s0t = lo + (n >> 1) * kTile, sa = s0t + (n & 1) * kHalf + 2 * lane;
+          pre_e[3 * i] = -1;
+          pre_e[3 * i + 1] = -1;
+          if (sa < hi) pre_e[3 * i] = page[sa];
+          if (sa + 1 < hi) pre_e[3 * i + 1] = page[sa + 1];
+          pre_e[3 * i + 2] = page[s0t];
+        }
+      }
+    }
     // the head's slice of wk for the [P;Q] build: requested now, used after the barrier
     if (wk_vec) {
       const int hk_pre = (h0 + (warp >> 2)) / gqa;
@@ -483,10 +504,10 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
     const bool issuer = (q4 & 1) == 0;  // warps 0 and 2 of the head request the copies
     if (issuer) {
       // the first kSlots units, so that the stream starts while [P;Q] is being built
-      for (int n = q4 >> 1; n < kSlots && n < n_units; n += 2) {
-        int e0, e1, first;
-        fetch_entries(n, e0, e1, first);
-        issue_unit(n, e0, e1, first);
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int n = (q4 >> 1) + 2 * i;
+        if (n < kSlots && n < n_units) issue_unit(n, pre_e[3 * i], pre_e[3 * i + 1], pre_e[3 * i + 2]);
       }
     }
 
