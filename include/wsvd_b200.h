@@ -153,6 +153,31 @@ int wsvd_decode_stage2(const float* mid_o, const float* lse, const int32_t* b_se
                        const void* wv, int64_t wv_stride_r, int32_t n_kv_heads, int32_t head_dim,
                        void* stream);
 
+/*
+ * The whole op for callers that cannot supply a workspace.  No counterpart in the
+ * reference (its wrapper always allocates mid_o with torch).
+ *
+ * Meant for hosts that must not, or cannot, allocate device memory around the call: an
+ * inference server whose KV-cache pool already owns all free HBM, a plugin invoked where a
+ * cudaMalloc would stall the device or upset the host's allocator bookkeeping, a bare C
+ * caller with no allocator.  The split-KV scratch (and the position table, when
+ * p->rope_table is NULL) is a fixed array of WSVD_STATIC_SCRATCH_BYTES inside the library;
+ * each GPU that loads the library keeps that much memory until the process exits.
+ *
+ *  - Same arguments, result and status codes as wsvd_latent_decode, minus the workspace.
+ *  - Returns WSVD_ERR_TOO_LARGE when wsvd_latent_decode_workspace_bytes(p) exceeds
+ *    WSVD_STATIC_SCRATCH_BYTES (pass a prebuilt rope_table to leave more room for
+ *    partials, or use wsvd_latent_decode).
+ *  - The first call on each device looks up the array's device address (one
+ *    cudaGetSymbolAddress, with the calling thread's current device); make that first call
+ *    before starting any stream capture.  No call allocates or frees memory.
+ *  - All calls on a device share the one array, which still holds the previous call's
+ *    partials; nothing in it needs clearing.  Two calls whose kernels can overlap on the
+ *    GPU (different streams, or concurrent host threads) race on it: serialise them.
+ */
+#define WSVD_STATIC_SCRATCH_BYTES (8u << 20)
+int wsvd_latent_decode_static(const WsvdLatentDecodeParams* p, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

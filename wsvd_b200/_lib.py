@@ -104,6 +104,7 @@ SYMBOLS = {
     "wsvd_latent_decode_plan": (ctypes.c_int, [_P, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]),
     "wsvd_latent_decode_workspace_bytes": (ctypes.c_size_t, [_P]),
     "wsvd_latent_decode": (ctypes.c_int, [_P, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    "wsvd_latent_decode_static": (ctypes.c_int, [_P, ctypes.c_void_p]),
     "wsvd_latent_decode_stage1": (ctypes.c_int, [_P, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p]),
     "wsvd_decode_stage2": (ctypes.c_int, [
         ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
