@@ -154,6 +154,28 @@ int wsvd_decode_stage2(const float* mid_o, const float* lse, const int32_t* b_se
                        void* stream);
 
 /*
+ * Dense f16 flash-decoding baseline on full K/V caches [T, Hkv, D] (K stored rotated, no
+ * RoPE in the kernel), same page-table interface and split-KV structure.
+ * Replaces token_decode_attention_flash_decoding (flash_decoding.py:98-131;
+ * flash_decoding_stage1.py:75-105, flash_decoding_stage2.py:48-64).  out: f16 [B,Hq,D].
+ */
+typedef struct WsvdDenseDecodeParams {
+  const void* q;            int64_t q_stride_b, q_stride_h;
+  const void* k;            int64_t k_stride_t, k_stride_h;     /* f16 [T, Hkv, D] */
+  const void* v;            int64_t v_stride_t, v_stride_h;
+  const int32_t* req_to_token; int64_t rtt_stride;
+  const int32_t* b_req_idx;
+  const int32_t* b_seq_len;
+  void* out;                int64_t out_stride_b, out_stride_h;
+  int32_t batch, n_q_heads, n_kv_heads, head_dim;
+  int32_t max_len;
+  int32_t split_len;        /* 0 = library default */
+  float sm_scale;           /* 0 = 1/sqrt(head_dim) */
+} WsvdDenseDecodeParams;
+size_t wsvd_dense_decode_workspace_bytes(const WsvdDenseDecodeParams* p);
+int wsvd_dense_decode_f16(const WsvdDenseDecodeParams* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * The whole op for callers that cannot supply a workspace.  No counterpart in the
  * reference (its wrapper always allocates mid_o with torch).
  *

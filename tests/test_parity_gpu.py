@@ -103,3 +103,76 @@ def test_f16_latents(kernel):
     got = op_f16(c.q, c.infer_state, 2, 128, c.latent_k, c.latent_v, c.wk, kernel=kernel)
     torch.cuda.synchronize()
     assert_close(got, oracle_for(case), "f16 latents")
+
+
+def _gold(name):
+    import os
+
+    import numpy as np
+
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", name))
+    return {k: torch.from_numpy(z[k]) for k in z.files}
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_reference_triton_int8_golden_gqa_int8_wk(kernel):
+    """Inputs and output of the reference's int8 Triton kernel (GQA, int8 wk + wk_scale,
+    shuffled page table).  The reference rounds to f16 inside, hence the wider tolerance."""
+    from wsvd_b200.infer_state import InferState
+
+    g = _gold("triton_i8_gqa_ragged_paged.npz")
+    B, Hq, D = g["q"].shape
+    st = InferState(B, g["req_to_token"].shape[1], g["b_seq_len"].tolist(), device="cuda",
+                    req_to_token=g["req_to_token"], b_req_idx=g["b_req_idx"])
+    got = op_i8(g["q"].cuda(), st, Hq, D, g["cache_latent_k"].cuda(), g["cache_latent_k_scale"].cuda(),
+                g["cache_latent_v"].cuda(), g["cache_latent_v_scale"].cuda(), g["wk"].cuda(), g["wk_scale"].cuda(),
+                kernel=kernel)
+    torch.cuda.synchronize()
+    assert ops.kernel_status() == 0
+    assert_close(got, g["out"].float(), "vs reference Triton int8 kernel", atol=4e-3, rtol=1e-2)
+
+
+def test_reference_triton_f16_golden():
+    from wsvd_b200.infer_state import InferState
+
+    g = _gold("triton_f16_ragged_paged.npz")
+    B, H, D = g["q"].shape
+    st = InferState(B, g["req_to_token"].shape[1], g["b_seq_len"].tolist(), device="cuda",
+                    req_to_token=g["req_to_token"], b_req_idx=g["b_req_idx"])
+    got = op_f16(g["q"].cuda(), st, H, D, g["cache_latent_k"].cuda(), g["cache_latent_v"].cuda(), g["wk"].cuda())
+    torch.cuda.synchronize()
+    assert_close(got, g["out"].float(), "vs reference Triton f16 kernel", atol=4e-3, rtol=1e-2)
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_interleaved_rope_layout(kernel):
+    case = inputs.make_case(2, 4, 128, 64, 64, [515, 130], 515, seed=77)
+    got = run_i8(case, kernel, rope_layout="interleaved")
+    assert_close(got, oracle_for(case, rope_layout="interleaved"), "interleaved pairing")
+
+
+def test_stage_level_wrappers_match_the_op():
+    """Reference-named stage 1 / stage 2 wrappers with caller-owned partial buffers."""
+    from wsvd_b200.kernel.flash_int8_latent_per_head_decoding_rope_stage1 import (
+        flash_int8_latent_per_head_decode_rope_stage1)
+    from wsvd_b200.kernel.flash_latent_per_head_decoding_stage2 import flash_decode_stage2
+
+    case = inputs.make_case(3, 4, 128, 64, 48, [700, 90, 1300], 1300, seed=8)
+    c = case.to("cuda")
+    s = c.infer_state
+    block_seq = 256
+    ns = (1300 + block_seq - 1) // block_seq
+    mid = torch.zeros(3, 4, ns, 48, dtype=torch.float32, device="cuda")
+    lse = torch.zeros(3, 4, ns, dtype=torch.float32, device="cuda")
+    out = torch.empty(3, 4, 48, dtype=torch.float16, device="cuda")
+    flash_int8_latent_per_head_decode_rope_stage1(c.q, c.latent_k, c.k_scale, c.latent_v, c.v_scale, c.wk, None,
+                                                  s.req_manager.req_to_token_indexs, s.b_req_idx, s.b_seq_len,
+                                                  s.max_len_in_batch, mid, lse, block_seq)
+    flash_decode_stage2(mid, lse, s.b_seq_len, out, block_seq)
+    torch.cuda.synchronize()
+    assert_close(out, oracle_for(case), "stage wrappers")
+    from oracle import latent_decode_oracle as orc
+    want_mid, want_lse = orc.latent_decode_stage1_oracle(*case.oracle_args(), block_seq=block_seq)
+    ok = ~torch.isnan(want_lse)
+    assert (mid.cpu()[ok] - want_mid[ok]).abs().max() < 2e-3
+    assert (lse.cpu()[ok] - want_lse[ok]).abs().max() < 2e-3

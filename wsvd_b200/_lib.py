@@ -90,6 +90,22 @@ class LatentDecodeParams(ctypes.Structure):
     ]
 
 
+class DenseDecodeParams(ctypes.Structure):
+    """ctypes mirror of WsvdDenseDecodeParams."""
+
+    _fields_ = [
+        ("q", ctypes.c_void_p), ("q_stride_b", ctypes.c_int64), ("q_stride_h", ctypes.c_int64),
+        ("k", ctypes.c_void_p), ("k_stride_t", ctypes.c_int64), ("k_stride_h", ctypes.c_int64),
+        ("v", ctypes.c_void_p), ("v_stride_t", ctypes.c_int64), ("v_stride_h", ctypes.c_int64),
+        ("req_to_token", ctypes.c_void_p), ("rtt_stride", ctypes.c_int64),
+        ("b_req_idx", ctypes.c_void_p), ("b_seq_len", ctypes.c_void_p),
+        ("out", ctypes.c_void_p), ("out_stride_b", ctypes.c_int64), ("out_stride_h", ctypes.c_int64),
+        ("batch", ctypes.c_int32), ("n_q_heads", ctypes.c_int32), ("n_kv_heads", ctypes.c_int32),
+        ("head_dim", ctypes.c_int32), ("max_len", ctypes.c_int32), ("split_len", ctypes.c_int32),
+        ("sm_scale", ctypes.c_float),
+    ]
+
+
 # name -> (restype, argtypes); every symbol include/wsvd_b200.h declares
 _P = ctypes.POINTER(LatentDecodeParams)
 SYMBOLS = {
@@ -104,6 +120,9 @@ SYMBOLS = {
     "wsvd_latent_decode_plan": (ctypes.c_int, [_P, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]),
     "wsvd_latent_decode_workspace_bytes": (ctypes.c_size_t, [_P]),
     "wsvd_latent_decode": (ctypes.c_int, [_P, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    "wsvd_dense_decode_workspace_bytes": (ctypes.c_size_t, [ctypes.POINTER(DenseDecodeParams)]),
+    "wsvd_dense_decode_f16": (ctypes.c_int, [ctypes.POINTER(DenseDecodeParams), ctypes.c_void_p, ctypes.c_size_t,
+                                             ctypes.c_void_p]),
     "wsvd_latent_decode_static": (ctypes.c_int, [_P, ctypes.c_void_p]),
     "wsvd_latent_decode_stage1": (ctypes.c_int, [_P, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p]),
     "wsvd_decode_stage2": (ctypes.c_int, [

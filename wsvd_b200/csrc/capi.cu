@@ -246,6 +246,66 @@ int wsvd_latent_decode_stage1(const WsvdLatentDecodeParams* p, float* mid_o, flo
   return run_stage1(a, nullptr, reinterpret_cast<cudaStream_t>(stream));
 }
 
+static void dense_plan(const WsvdDenseDecodeParams* p, int* sl, int* ns) {
+  int len = p->split_len;
+  if (len <= 0) {
+    const long items = (long)p->batch * p->n_q_heads;
+    long want = items > 0 ? (148L * 16 + items - 1) / items : 1;
+    if (want < 1) want = 1;
+    long l = (p->max_len + want - 1) / want;
+    l = ((l + 63) / 64) * 64;
+    if (l < 256) l = 256;
+    len = (int)l;
+  }
+  *sl = len;
+  int n = (p->max_len + len - 1) / len;
+  *ns = n < 1 ? 1 : n;
+}
+
+size_t wsvd_dense_decode_workspace_bytes(const WsvdDenseDecodeParams* p) {
+  if (!p || p->batch < 0 || p->n_q_heads <= 0 || p->head_dim <= 0 || p->max_len < 0 || p->split_len < 0) return 0;
+  int sl, ns;
+  dense_plan(p, &sl, &ns);
+  return (size_t)p->batch * p->n_q_heads * ns * ((size_t)p->head_dim + 1) * sizeof(float);
+}
+
+int wsvd_dense_decode_f16(const WsvdDenseDecodeParams* p, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!p) return WSVD_ERR_NULL_POINTER;
+  if (!p->q || !p->k || !p->v || !p->req_to_token || !p->b_req_idx || !p->b_seq_len || !p->out)
+    return WSVD_ERR_NULL_POINTER;
+  if (!is_pow2_dim(p->head_dim)) return WSVD_ERR_BAD_SHAPE;
+  if (p->batch < 0 || p->max_len < 0 || p->split_len < 0) return WSVD_ERR_BAD_SHAPE;
+  if (p->n_q_heads <= 0 || p->n_kv_heads <= 0 || p->n_q_heads % p->n_kv_heads != 0) return WSVD_ERR_BAD_SHAPE;
+  if (p->batch > 65535 || p->n_q_heads > 65535) return WSVD_ERR_TOO_LARGE;
+  // 16-byte row loads
+  if (p->head_dim >= 64 && (!aligned16(p->k) || !aligned16(p->v) || p->k_stride_t % 8 || p->k_stride_h % 8 ||
+                            p->v_stride_t % 8 || p->v_stride_h % 8))
+    return WSVD_ERR_BAD_STRIDE;
+  if (p->batch == 0) return WSVD_OK;
+  if (!workspace) return WSVD_ERR_NULL_POINTER;
+  if (workspace_bytes < wsvd_dense_decode_workspace_bytes(p)) return WSVD_ERR_WORKSPACE_TOO_SMALL;
+  if (!aligned16(workspace)) return WSVD_ERR_BAD_STRIDE;
+  int sl, ns;
+  dense_plan(p, &sl, &ns);
+  wsvd::DenseArgs a;
+  a.q = reinterpret_cast<const __half*>(p->q); a.q_stride_b = p->q_stride_b; a.q_stride_h = p->q_stride_h;
+  a.k = reinterpret_cast<const __half*>(p->k); a.k_stride_t = p->k_stride_t; a.k_stride_h = p->k_stride_h;
+  a.v = reinterpret_cast<const __half*>(p->v); a.v_stride_t = p->v_stride_t; a.v_stride_h = p->v_stride_h;
+  a.req_to_token = p->req_to_token; a.rtt_stride = p->rtt_stride;
+  a.b_req_idx = p->b_req_idx; a.b_seq_len = p->b_seq_len;
+  a.mid_o = reinterpret_cast<float*>(workspace);
+  a.lse = a.mid_o + (size_t)p->batch * p->n_q_heads * ns * p->head_dim;
+  a.batch = p->batch; a.n_q_heads = p->n_q_heads; a.n_kv_heads = p->n_kv_heads; a.head_dim = p->head_dim;
+  a.split_len = sl; a.n_splits = ns;
+  a.sm_scale = p->sm_scale != 0.f ? p->sm_scale : (float)(1.0 / sqrt((double)p->head_dim));
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  cudaError_t e = wsvd::launch_dense_stage1(a, s);
+  if (e != cudaSuccess) return cuda_fail(e);
+  e = wsvd::launch_stage2(a.mid_o, a.lse, p->b_seq_len, p->out, p->out_stride_b, p->out_stride_h, p->batch,
+                          p->n_q_heads, ns, p->head_dim, sl, nullptr, 0, 1, p->head_dim, s);
+  return e == cudaSuccess ? WSVD_OK : cuda_fail(e);
+}
+
 int wsvd_decode_stage2(const float* mid_o, const float* lse, const int32_t* b_seq_len, void* out,
                        int64_t out_stride_b, int64_t out_stride_h, int32_t batch, int32_t n_q_heads,
                        int32_t n_splits, int32_t width, int32_t split_len, const void* wv, int64_t wv_stride_r,

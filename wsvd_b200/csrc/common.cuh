@@ -22,6 +22,20 @@ struct KArgs {
   float sm_scale;
 };
 
+// Kernel argument block of the dense baseline.
+struct DenseArgs {
+  const __half* q;  int64_t q_stride_b, q_stride_h;
+  const __half* k;  int64_t k_stride_t, k_stride_h;
+  const __half* v;  int64_t v_stride_t, v_stride_h;
+  const int32_t* req_to_token; int64_t rtt_stride;
+  const int32_t* b_req_idx;
+  const int32_t* b_seq_len;
+  float* mid_o;
+  float* lse;
+  int32_t batch, n_q_heads, n_kv_heads, head_dim, split_len, n_splits;
+  float sm_scale;
+};
+
 __device__ __forceinline__ float to_float(int8_t v) { return static_cast<float>(v); }
 __device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
 
@@ -43,6 +57,7 @@ cudaError_t launch_rope_table(void* table, int rows, const KArgs& a, cudaStream_
 size_t rope_table_bytes(int rows);
 cudaError_t read_tc_status(unsigned int* out);
 cudaError_t reset_tc_status();
+cudaError_t launch_dense_stage1(const DenseArgs& a, cudaStream_t stream);
 cudaError_t launch_stage2(const float* mid_o, const float* lse, const int32_t* b_seq_len, void* out,
                           int64_t out_stride_b, int64_t out_stride_h, int batch, int n_q_heads, int n_splits,
                           int width, int split_len, const void* wv, int64_t wv_stride_r, int n_kv_heads,

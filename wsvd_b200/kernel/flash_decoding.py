@@ -59,3 +59,15 @@ def token_decode_attention_flash_latent_per_head_decoding_rope(
         q3, infer_state, cache_latent_k, None, cache_latent_v, None, wk, None, wv=wv, out=out,
         workspace=workspace, alloc_tensor_func=alloc_tensor_func, pos_offset=pos_offset, theta=theta,
         rope_layout=rope_layout, split_len=split_len, kernel=kernel, stream=stream)
+
+
+def token_decode_attention_flash_decoding(
+    q, infer_state, q_head_num, head_dim, cache_k, cache_v, out=None, alloc_tensor_func=torch.empty, *,
+    workspace=None, split_len: int = 0, stream=None,
+):
+    """Dense f16 flash-decoding on full K/V caches [T, Hkv, D] (flash_decoding.py:98-131):
+    the reference's own "Flash Decoding" baseline, here as a CUDA kernel of the same
+    split-KV structure."""
+    q3 = q.view(infer_state.batch_size, q_head_num, head_dim)
+    return ops.dense_decode(q3, infer_state, cache_k, cache_v, out=out, alloc_tensor_func=alloc_tensor_func,
+                            workspace=workspace, split_len=split_len, stream=stream)

@@ -243,3 +243,43 @@ def decode_stage2(mid_out, mid_out_lse, b_seq_len, out, block_seq, *, wv=None, n
         check(_lib.lib().wsvd_decode_stage2(
             _ptr(mid_out), _ptr(mid_out_lse), _ptr(b_seq_len), _ptr(out), out.stride(0), out.stride(1),
             B, Hq, ns, W, int(block_seq), _ptr(wv), wv_stride, hkv, head_dim, _stream(stream)), "wsvd_decode_stage2")
+
+
+@torch.no_grad()
+def dense_decode(q, infer_state, cache_k, cache_v, out=None, alloc_tensor_func: Callable = torch.empty,
+                 workspace=None, split_len=0, stream=None):
+    """Dense f16 flash-decoding baseline: q [B,Hq,D], caches [T,Hkv,D] f16 -> [B,Hq,D] f16."""
+    from ._lib import DenseDecodeParams
+
+    _cuda_tensor("q", q, (torch.float16,), 3)
+    B, Hq, D = q.shape
+    _cuda_tensor("cache_k", cache_k, (torch.float16,), 3)
+    _cuda_tensor("cache_v", cache_v, (torch.float16,), 3)
+    Hkv = cache_k.shape[1]
+    _need(cache_k.shape[2] == D and cache_v.shape[2] == D, "q and K/V disagree on head_dim")
+    _need(cache_v.shape[1] == Hkv and Hq % Hkv == 0, "bad head counts")
+    _need(D in (16, 32, 64, 128), f"head_dim {D} not in {{16, 32, 64, 128}}")
+    rtt = infer_state.req_manager.req_to_token_indexs
+    _cuda_tensor("b_seq_len", infer_state.b_seq_len, (torch.int32,), 1)
+    _cuda_tensor("b_req_idx", infer_state.b_req_idx, (torch.int32,), 1)
+    _cuda_tensor("req_to_token_indexs", rtt, (torch.int32,), 2)
+    if out is None:
+        out = alloc_tensor_func((B, Hq, D), dtype=q.dtype, device=q.device)
+    _cuda_tensor("out", out, (torch.float16,), 3)
+    p = DenseDecodeParams()
+    p.q, p.q_stride_b, p.q_stride_h = q.data_ptr(), q.stride(0), q.stride(1)
+    p.k, p.k_stride_t, p.k_stride_h = cache_k.data_ptr(), cache_k.stride(0), cache_k.stride(1)
+    p.v, p.v_stride_t, p.v_stride_h = cache_v.data_ptr(), cache_v.stride(0), cache_v.stride(1)
+    p.req_to_token, p.rtt_stride = rtt.data_ptr(), rtt.stride(0)
+    p.b_req_idx, p.b_seq_len = infer_state.b_req_idx.data_ptr(), infer_state.b_seq_len.data_ptr()
+    p.out, p.out_stride_b, p.out_stride_h = out.data_ptr(), out.stride(0), out.stride(1)
+    p.batch, p.n_q_heads, p.n_kv_heads, p.head_dim = B, Hq, Hkv, D
+    p.max_len, p.split_len = int(infer_state.max_len_in_batch), int(split_len)
+    need = int(_lib.lib().wsvd_dense_decode_workspace_bytes(ctypes.byref(p)))
+    if workspace is None:
+        workspace = alloc_tensor_func(((need + 3) // 4,), dtype=torch.float32, device=q.device)
+    have = workspace.numel() * workspace.element_size()
+    with torch.cuda.device(q.device):
+        check(_lib.lib().wsvd_dense_decode_f16(ctypes.byref(p), _ptr(workspace), have, _stream(stream)),
+              "wsvd_dense_decode_f16")
+    return out
