@@ -38,6 +38,11 @@ def _cuda_tensor(name, t, dtypes, ndim, inner_contiguous=True):
 
 
 _TABLES = {}
+_CALLS = {}
+
+
+def _sig(t):
+    return None if t is None else (t.data_ptr(), tuple(t.shape), tuple(t.stride()), t.dtype)
 
 
 def rope_table(device, positions: int, head_dim: int = 128, theta: float = 10000.0):
@@ -181,15 +186,30 @@ def latent_decode(
     at least workspace_bytes(); when absent it is taken from `alloc_tensor_func`."""
     B = int(infer_state.batch_size)
     q3 = q.view(B, q.shape[-2], q.shape[-1]) if q.dim() != 3 else q
-    p, keep = build_params(
-        q3, infer_state.b_seq_len, infer_state.b_req_idx, infer_state.req_manager.req_to_token_indexs,
-        int(infer_state.max_len_in_batch), latent_k, k_scale, latent_v, v_scale, wk, wk_scale, wv=wv, out=out,
-        pos_offset=pos_offset, theta=theta, rope_layout=rope_layout, split_len=split_len, kernel=kernel)
+    rtt = infer_state.req_manager.req_to_token_indexs
+    max_len = int(infer_state.max_len_in_batch)
+    # A decode loop calls with the same buffers every step: the validated argument block
+    # is kept per set of (address, shape, stride) and options.
+    key = (_sig(q3), _sig(infer_state.b_seq_len), _sig(infer_state.b_req_idx), _sig(rtt), max_len, _sig(latent_k),
+           _sig(k_scale), _sig(latent_v), _sig(v_scale), _sig(wk), _sig(wk_scale), _sig(wv), _sig(pos_offset),
+           float(theta), rope_layout, int(split_len), kernel)
+    hit = _CALLS.get(key)
+    if hit is None:
+        p, keep = build_params(
+            q3, infer_state.b_seq_len, infer_state.b_req_idx, rtt, max_len, latent_k, k_scale, latent_v, v_scale,
+            wk, wk_scale, wv=wv, out=None, pos_offset=pos_offset, theta=theta, rope_layout=rope_layout,
+            split_len=split_len, kernel=kernel)
+        if len(_CALLS) >= 64:
+            _CALLS.clear()
+        hit = _CALLS[key] = (p, workspace_bytes(p))
+    p, need = hit
+    out_w = p.head_dim if wv is not None else p.rank_v
     if out is None:
-        out_w = p.head_dim if wv is not None else p.rank_v
         out = alloc_tensor_func((B, p.n_q_heads, out_w), dtype=q.dtype, device=q.device)
-        p.out, p.out_stride_b, p.out_stride_h = out.data_ptr(), out.stride(0), out.stride(1)
-    need = workspace_bytes(p)
+    else:
+        _cuda_tensor("out", out, (torch.float16,), 3)
+        _need(tuple(out.shape) == (B, p.n_q_heads, out_w), f"out must be {(B, p.n_q_heads, out_w)}")
+    p.out, p.out_stride_b, p.out_stride_h = out.data_ptr(), out.stride(0), out.stride(1)
     if workspace is None:
         workspace = alloc_tensor_func(((need + 3) // 4,), dtype=torch.float32, device=q.device)
     else:
