@@ -159,6 +159,7 @@ def main():
     ap.add_argument("--kernel", default="auto", choices=["auto", "generic", "tc"])
     ap.add_argument("--split-len", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-dense", action="store_true", help="skip the dense f16 baseline kernel timing")
     args = ap.parse_args()
 
     from wsvd_b200 import inputs
@@ -329,6 +330,28 @@ def main():
             "kernel_status": ops.kernel_status(),
             "clocks": clocks,
         }
+        if world == 1 and not args.no_dense:
+            # dense f16 flash-decoding of the same shape (K/V [T,H,128] f16, 512 B per token-head)
+            from wsvd_b200.infer_state import InferState as _IS
+            from wsvd_b200.kernel.flash_decoding import token_decode_attention_flash_decoding as dense_op
+            S = spec.max_len
+            kd = torch.randn(B, H, S, D, dtype=torch.float16, device=dev)
+            vd = torch.randn(B, H, S, D, dtype=torch.float16, device=dev)
+            kv = kd.as_strided(((B - 1) * H * S + S, H, D), (D, S * D, 1))
+            vv = vd.as_strided(((B - 1) * H * S + S, H, D), (D, S * D, 1))
+            dst = _IS(B, S, lens, device=dev, req_to_token=st.req_manager.req_to_token_indexs)
+            dout = torch.empty(B, H, D, dtype=torch.float16, device=dev)
+            dws = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
+            dense = lambda: dense_op(case.q, dst, H, D, kv, vv, out=dout, workspace=dws)
+            for _ in range(3):
+                dense()
+            ms_dense = timed(dense, max(5, args.steps // 2)) / max(5, args.steps // 2)
+            dense_bytes = sum(lens) * H * 4 * D
+            line["dense_f16_baseline"] = {
+                "us_per_layer": ms_dense * 1e3, "GB/s": dense_bytes / (ms_dense * 1e-3) / 1e9,
+                "bytes_per_token_head": 4 * D, "latent_speedup": ms_dense / ms_step,
+                "byte_reduction": 4 * D / (spec.rank_k + spec.rank_v + 4)}
+            del kd, vd
         if world == 1 and not args.no_cpu_baseline:
             cb = cpu_reference_run(spec, steps=3, warmup=1)
             line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
