@@ -93,6 +93,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive_n(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
@@ -461,8 +464,7 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
           mbar_expect_tx(bar_full(stage), unit_tx);
           tma_load_3d(sRing + stage * kUnitBytes, &ta.tmap_k, 0, c1, c2, bar_full(stage));
           tma_load_3d(sRing + stage * kUnitBytes + kKBytes, &ta.tmap_v, 0, c1, c2, bar_full(stage));
-        } else {
-          mbar_arrive(bar_full(stage));
+          mbar_arrive_n(bar_full(stage), 31);  // the arrivals the gather path makes lane by lane
         }
       } else {
         // Gather through the page table: lane (r0 = lane/4, c = lane%4) copies 16-byte chunk
@@ -624,13 +626,21 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       if (q4 == 0) WSVD_TRACE(2 + g, t, 1);
       ok = wait_issued(stage, nth / kSlots + 1) && mbar_wait(bar_full(stage), (nth / kSlots) & 1);
       if (q4 == 0) WSVD_TRACE(2 + g, t, 2);
-      ok = ok && mbar_wait(bar_w_full(buf), (t >> 1) & 1);
-      if (q4 == 0) WSVD_TRACE(2 + g, t, 3);
       if (!ok) break;
-      tc_fence_after();
 
-      // ---- V rows of this warp's 32 tokens into registers (lane (rg, tg): chunk rg of rows
-      //      tg + 8k), so that the ring slot can be handed back right after the score
+      // ---- the warp's 32 K rows (lane = token) and V rows (lane (rg, tg): chunk rg of rows
+      //      tg + 8k) go to registers at once, so that the ring slot is handed back and
+      //      refilled before any arithmetic: the register file is the second buffer stage
+      uint4 kreg[4];
+      {
+        const uint32_t krow = sRing + stage * kUnitBytes + (row & (kHalf - 1)) * 64;
+        const uint32_t sw = (row >> 1) & 3;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(kreg[c].x), "=r"(kreg[c].y), "=r"(kreg[c].z), "=r"(kreg[c].w)
+                       : "r"(krow + ((c ^ sw) << 4)));
+      }
       if (pv_on) {
         const uint32_t vsm = sRing + stage * kUnitBytes + kKBytes + ((q4 & 1) * 32 + tg) * Rv + rg * 16;
 #pragma unroll
@@ -639,30 +649,36 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
                        : "=r"(v_cur[k].x), "=r"(v_cur[k].y), "=r"(v_cur[k].z), "=r"(v_cur[k].w)
                        : "r"(vsm + k * 8 * Rv));
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_empty(stage));
+      if (issuer && n_issue < n_units) {
+        // once the pair's other warp has let go of the slot too, refill it
+        if (!mbar_wait(bar_empty(stage), (nth / kSlots) & 1)) {
+          ok = false;
+          break;
+        }
+        issue_unit(n_issue, ie0, ie1, ifirst);
+      }
+
+      ok = mbar_wait(bar_w_full(buf), (t >> 1) & 1);
+      if (q4 == 0) WSVD_TRACE(2 + g, t, 3);
+      if (!ok) break;
+      tc_fence_after();
 
       // ---- score: dot of this token's int8 K row with its row of W, in two halves of 32
       //      ranks, four independent accumulators
-      const uint32_t krow = sRing + stage * kUnitBytes + (row & (kHalf - 1)) * 64;
-      const uint32_t sw = (row >> 1) & 3;
       const uint32_t taddr = tmem + ((uint32_t)(q4 * 32) << 16) + buf * (kG * kRk) + g * kRk;
       uint64_t dot[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
         uint32_t w[2][16];
-        uint4 kw[2];
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          const int c = 2 * hf + cc;
-          tmem_ld16(taddr + c * 16, w[cc]);
-          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                       : "=r"(kw[cc].x), "=r"(kw[cc].y), "=r"(kw[cc].z), "=r"(kw[cc].w)
-                       : "r"(krow + ((c ^ sw) << 4)));
-        }
+        for (int cc = 0; cc < 2; ++cc) tmem_ld16(taddr + (2 * hf + cc) * 16, w[cc]);
         tmem_wait_ld();
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
-          const uint32_t kws[4] = {kw[cc].x ^ 0x80808080u, kw[cc].y ^ 0x80808080u, kw[cc].z ^ 0x80808080u,
-                                   kw[cc].w ^ 0x80808080u};
+          const uint4 kq = kreg[2 * hf + cc];
+          const uint32_t kws[4] = {kq.x ^ 0x80808080u, kq.y ^ 0x80808080u, kq.z ^ 0x80808080u, kq.w ^ 0x80808080u};
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             uint64_t x01, x23;
@@ -676,18 +692,7 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       const uint64_t dot2 = add2(add2(dot[0], dot[1]), add2(dot[2], dot[3]));
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(bar_w_empty(buf));   // this warp has read its rows of W ...
-        mbar_arrive(bar_empty(stage));   // ... and its K and V rows
-      }
-      if (issuer && n_issue < n_units) {
-        // once the pair's other warp has let go of the slot too, refill it
-        if (!mbar_wait(bar_empty(stage), (nth / kSlots) & 1)) {
-          ok = false;
-          break;
-        }
-        issue_unit(n_issue, ie0, ie1, ifirst);
-      }
+      if (lane == 0) mbar_arrive(bar_w_empty(buf));  // this warp has read its rows of W
       if (q4 == 0) WSVD_TRACE(2 + g, t, 4);
       float d0, d1;
       upk(dot2, d0, d1);
