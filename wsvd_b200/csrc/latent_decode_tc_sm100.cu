@@ -41,7 +41,8 @@ constexpr int kTile = 128;     // positions per MMA tile (= tensor-memory lanes)
 constexpr int kRk = 64;
 constexpr int kEpiWarps = 4 * kG;
 constexpr int kMmaWarp = kEpiWarps;
-constexpr int kThreads = (kEpiWarps + 1) * 32;
+constexpr int kProducers = 3;   // copy-issuing warps; with the MMA warp they fill one warp slot per scheduler
+constexpr int kThreads = (kEpiWarps + 1 + kProducers) * 32;
 // Latent ring: every head owns kSlots slots, each holding half a tile (64 tokens): K rows
 // at a 64-byte pitch followed by V rows at a rank_v pitch.  A slot is only ever reused by
 // the same head, whose warps consume their slots in order; with slots shared between heads
@@ -312,7 +313,6 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
   const bool wk_vec = p.wk_dtype == WSVD_F16 && (p.wk_stride_r & 7) == 0 &&
                       (reinterpret_cast<uintptr_t>(p.wk) & 15) == 0;
   uint4 wpre[8];
-  int pre_e[6] = {-1, -1, 0, -1, -1, 0};
 
   // ---- set-up: barriers + tensor memory (MMA warp), scaled q to shared memory (epilogue warps)
   if (warp == kMmaWarp) {
@@ -339,22 +339,6 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
     if (ta.use_tma && warp == 0 && lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&ta.tmap_k)) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&ta.tmap_v)) : "memory");
-    }
-    // page entries of the first ring units (requested now, used after the barrier)
-    if ((warp & 1) == 0) {
-      const int nq = (warp & 3) >> 1;  // issuing warp 0 of the head starts units 0 and 2, warp 2 unit 1
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int n = nq + 2 * i;
-        if (n < kSlots && n < 2 * ntiles) {
-          const int s0t = lo + (n >> 1) * kTile, sa = s0t + (n & 1) * kHalf + 2 * lane;
-          pre_e[3 * i] = -1;
-          pre_e[3 * i + 1] = -1;
-          if (sa < hi) pre_e[3 * i] = page[sa];
-          if (sa + 1 < hi) pre_e[3 * i + 1] = page[sa + 1];
-          pre_e[3 * i + 2] = page[s0t];
-        }
-      }
     }
     // the head's slice of wk for the [P;Q] build: requested now, used after the barrier
     if (wk_vec) {
@@ -429,19 +413,13 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       if (!ok) atomicMax(&g_status, (unsigned)kTimeoutMma);
     }
     __syncwarp();
-  } else if (warp < 4 * G) {
-    // ================================================================= epilogue
-    const int g = warp >> 2, q4 = warp & 3;
-    const int h = h0 + g, hk = h / gqa;
-    const int row = q4 * 32 + lane;
-    const bool interleaved = p.rope_layout == WSVD_ROPE_INTERLEAVED;
-
-    // ---- latent copies.  The head's half-tiles (units n = 2*tile + half) cycle through
-    //      its kSlots ring slots.  Unit n is requested by the first warp of the pair that
-    //      consumed unit n - kSlots, as soon as that pair has handed the slot back, so every
-    //      head streams independently of the others.
-    const uint8_t* kbase = reinterpret_cast<const uint8_t*>(p.latent_k) + (int64_t)hk * p.k_stride_h;
-    const uint8_t* vbase_g = reinterpret_cast<const uint8_t*>(p.latent_v) + (int64_t)hk * p.v_stride_h;
+  } else if (warp > kMmaWarp) {
+    // ================================================================= latent copies
+    // Every head's half-tiles (units n = 2*tile + half) cycle through its kSlots ring slots.
+    // The units of all heads, taken n-major, are dealt out to the producer warps in turn;
+    // unit n of a head is requested as soon as the pair of epilogue warps that consumed
+    // unit n - kSlots has handed the slot back.
+    const int pw = warp - kMmaWarp - 1;
     const uint32_t unit_tx = kKBytes + kHalf * Rv;
     const int n_units = 2 * ntiles;
     // page entries of the unit's 64 rows (two per lane) and of its tile's first row
@@ -453,8 +431,8 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       if (sa + 1 < hi) e1 = page[sa + 1];
       first = page[s0t];
     };
-    auto issue_unit = [&](int n, int e0, int e1, int first) {
-      const int stage = g * kSlots + n % kSlots;
+    auto issue_unit = [&](int n, int g, int stage, int use, int e0, int e1, int first) {
+      const int hk = (h0 + g) / gqa;
       const int sl0 = first + (n & 1) * kHalf;  // slot of the unit's first row if the tile is affine
       const bool affine = (e0 < 0 || e0 == sl0 + 2 * lane) && (e1 < 0 || e1 == sl0 + 2 * lane + 1);
       if (ta.use_tma && __all_sync(0xffffffffu, affine)) {
@@ -470,6 +448,8 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
         // Gather through the page table: lane (r0 = lane/4, c = lane%4) copies 16-byte chunk
         // c of rows r0 + 8k.  K chunks are XOR-swizzled with (row/2)%4 exactly as the TMA
         // 64-byte swizzle places them; (row/2)%4 does not depend on k.
+        const uint8_t* kbase = reinterpret_cast<const uint8_t*>(p.latent_k) + (int64_t)hk * p.k_stride_h;
+        const uint8_t* vbase_g = reinterpret_cast<const uint8_t*>(p.latent_v) + (int64_t)hk * p.v_stride_h;
         const int c = lane & 3, r0 = lane >> 2;
         const uint32_t dst = sRing + stage * kUnitBytes;
         const uint32_t doff_k = r0 * 64 + ((c ^ ((r0 >> 1) & 3)) << 4);
@@ -490,9 +470,47 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       // consumed, so from then on the parity wait cannot be a phase ahead or behind.
       __syncwarp();
       if (lane == 0)
-        asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(sbase + kOffIssued + 4u * stage), "r"(n / kSlots + 1)
+        asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(sbase + kOffIssued + 4u * stage), "r"(use + 1)
                      : "memory");
     };
+    // this warp's units: every kProducers-th of the sequence (n, g), g running fastest
+    auto advance = [&](int& n, int& g) {
+      g += kProducers;
+      while (g >= G) {
+        g -= G;
+        ++n;
+      }
+    };
+    int n = 0, g = pw - kProducers;
+    advance(n, g);
+    int e0 = -1, e1 = -1, first = 0;
+    if (n < n_units) fetch_entries(n, e0, e1, first);
+    bool ok = true;
+    while (n < n_units) {
+      int n2 = n, g2 = g;
+      advance(n2, g2);
+      int f0 = -1, f1 = -1, ffirst = 0;
+      if (n2 < n_units) fetch_entries(n2, f0, f1, ffirst);  // the next unit's entries, a unit ahead
+      const int use = n / kSlots, stage = g * kSlots + (n - use * kSlots);
+      if (use > 0) {
+        ok = mbar_wait(bar_empty(stage), (use - 1) & 1);
+        if (!ok) break;
+      }
+      issue_unit(n, g, stage, use, e0, e1, first);
+      n = n2;
+      g = g2;
+      e0 = f0;
+      e1 = f1;
+      first = ffirst;
+    }
+    if (!ok) atomicMax(&g_status, (unsigned)kTimeoutProducer);
+  } else if (warp < 4 * G) {
+    // ================================================================= epilogue
+    const int g = warp >> 2, q4 = warp & 3;
+    const int h = h0 + g, hk = h / gqa;
+    const int row = q4 * 32 + lane;
+    const bool interleaved = p.rope_layout == WSVD_ROPE_INTERLEAVED;
+
     auto wait_issued = [&](int stage, int uses) -> bool {
       const uint32_t addr = sbase + kOffIssued + 4u * stage;
       const uint64_t t0 = global_ns();
@@ -503,16 +521,6 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
         if (global_ns() - t0 > 2000000000ull) return false;
       }
     };
-    const bool issuer = (q4 & 1) == 0;  // warps 0 and 2 of the head request the copies
-    if (issuer) {
-      // the first kSlots units, so that the stream starts while [P;Q] is being built
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int n = (q4 >> 1) + 2 * i;
-        if (n < kSlots && n < n_units) issue_unit(n, pre_e[3 * i], pre_e[3 * i + 1], pre_e[3 * i + 2]);
-      }
-    }
-
     // ---- B operand: P (cos coefficients) and Q (sin coefficients) of this head, f16,
     //      rows n = g*64 + r, 64 frequencies per row, 128-byte swizzle
     {
@@ -620,9 +628,6 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       if (q4 == 0) WSVD_TRACE(2 + g, t, 0);
       load_scales(slot_n, sk_n, sv_n);
       load_slot(s + 2 * kTile, slot_n);
-      const int n_issue = nth + kSlots;  // the unit that will reuse this warp's slot
-      int ie0 = -1, ie1 = -1, ifirst = 0;
-      if (issuer && n_issue < n_units) fetch_entries(n_issue, ie0, ie1, ifirst);
       if (q4 == 0) WSVD_TRACE(2 + g, t, 1);
       ok = wait_issued(stage, nth / kSlots + 1) && mbar_wait(bar_full(stage), (nth / kSlots) & 1);
       if (q4 == 0) WSVD_TRACE(2 + g, t, 2);
@@ -651,14 +656,6 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_empty(stage));
-      if (issuer && n_issue < n_units) {
-        // once the pair's other warp has let go of the slot too, refill it
-        if (!mbar_wait(bar_empty(stage), (nth / kSlots) & 1)) {
-          ok = false;
-          break;
-        }
-        issue_unit(n_issue, ie0, ie1, ifirst);
-      }
 
       ok = mbar_wait(bar_w_full(buf), (t >> 1) & 1);
       if (q4 == 0) WSVD_TRACE(2 + g, t, 3);
