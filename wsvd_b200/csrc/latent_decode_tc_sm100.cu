@@ -416,9 +416,11 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
   } else if (warp > kMmaWarp) {
     // ================================================================= latent copies
     // Every head's half-tiles (units n = 2*tile + half) cycle through its kSlots ring slots.
-    // The units of all heads, taken n-major, are dealt out to the producer warps in turn;
-    // unit n of a head is requested as soon as the pair of epilogue warps that consumed
-    // unit n - kSlots has handed the slot back.
+    // Producer warp pw owns ring slot pw of every head, i.e. the units n = pw (mod kSlots).
+    // Unit n of a head is requested as soon as the pair of epilogue warps that consumed unit
+    // n - kSlots has handed the slot back.  On the TMA path lane g serves head g on its own:
+    // it waits for that head's slot and issues the two copies, so the heads do not queue
+    // behind one another.
     const int pw = warp - kMmaWarp - 1;
     const uint32_t unit_tx = kKBytes + kHalf * Rv;
     const int n_units = 2 * ntiles;
@@ -431,74 +433,66 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       if (sa + 1 < hi) e1 = page[sa + 1];
       first = page[s0t];
     };
-    auto issue_unit = [&](int n, int g, int stage, int use, int e0, int e1, int first) {
-      const int hk = (h0 + g) / gqa;
+    // Publishing "unit `use` of this slot has been requested": a consumer waits for this
+    // before it waits on the slot's mbarrier.  The request is made only after the slot's
+    // previous unit was consumed, so from then on the parity wait cannot be a phase ahead
+    // or behind.
+    auto publish = [&](int stage, int use) {
+      asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(sbase + kOffIssued + 4u * stage), "r"(use + 1) : "memory");
+    };
+    int e0 = -1, e1 = -1, first = 0;
+    if (pw < n_units) fetch_entries(pw, e0, e1, first);
+    bool ok = true;
+    int use = 0;
+    for (int n = pw; n < n_units && ok; n += kSlots, ++use) {
+      int f0 = -1, f1 = -1, ffirst = 0;
+      if (n + kSlots < n_units) fetch_entries(n + kSlots, f0, f1, ffirst);  // the next unit's, one unit ahead
       const int sl0 = first + (n & 1) * kHalf;  // slot of the unit's first row if the tile is affine
       const bool affine = (e0 < 0 || e0 == sl0 + 2 * lane) && (e1 < 0 || e1 == sl0 + 2 * lane + 1);
       if (ta.use_tma && __all_sync(0xffffffffu, affine)) {
-        // two TMA copies of 64 consecutive token slots; lane 0's expect_tx is its arrival
-        if (lane == 0) {
-          const int c1 = ta.slot_axis == 1 ? sl0 : hk, c2 = ta.slot_axis == 1 ? hk : sl0;
-          mbar_expect_tx(bar_full(stage), unit_tx);
-          tma_load_3d(sRing + stage * kUnitBytes, &ta.tmap_k, 0, c1, c2, bar_full(stage));
-          tma_load_3d(sRing + stage * kUnitBytes + kKBytes, &ta.tmap_v, 0, c1, c2, bar_full(stage));
-          mbar_arrive_n(bar_full(stage), 31);  // the arrivals the gather path makes lane by lane
+        // two TMA copies of 64 consecutive token slots per head
+        if (lane < G) {
+          const int stage = lane * kSlots + pw, hk = (h0 + lane) / gqa;
+          if (use > 0) ok = mbar_wait(bar_empty(stage), (use - 1) & 1);
+          if (ok) {
+            const int c1 = ta.slot_axis == 1 ? sl0 : hk, c2 = ta.slot_axis == 1 ? hk : sl0;
+            mbar_expect_tx(bar_full(stage), unit_tx);
+            tma_load_3d(sRing + stage * kUnitBytes, &ta.tmap_k, 0, c1, c2, bar_full(stage));
+            tma_load_3d(sRing + stage * kUnitBytes + kKBytes, &ta.tmap_v, 0, c1, c2, bar_full(stage));
+            mbar_arrive_n(bar_full(stage), 31);  // the arrivals the gather path makes lane by lane
+            publish(stage, use);
+          }
         }
+        ok = __all_sync(0xffffffffu, ok);
       } else {
-        // Gather through the page table: lane (r0 = lane/4, c = lane%4) copies 16-byte chunk
-        // c of rows r0 + 8k.  K chunks are XOR-swizzled with (row/2)%4 exactly as the TMA
-        // 64-byte swizzle places them; (row/2)%4 does not depend on k.
-        const uint8_t* kbase = reinterpret_cast<const uint8_t*>(p.latent_k) + (int64_t)hk * p.k_stride_h;
-        const uint8_t* vbase_g = reinterpret_cast<const uint8_t*>(p.latent_v) + (int64_t)hk * p.v_stride_h;
+        // Gather through the page table, head after head: lane (r0 = lane/4, c = lane%4)
+        // copies 16-byte chunk c of rows r0 + 8k.  K chunks are XOR-swizzled with (row/2)%4
+        // exactly as the TMA 64-byte swizzle places them; (row/2)%4 does not depend on k.
         const int c = lane & 3, r0 = lane >> 2;
-        const uint32_t dst = sRing + stage * kUnitBytes;
         const uint32_t doff_k = r0 * 64 + ((c ^ ((r0 >> 1) & 3)) << 4);
         const uint32_t doff_v = kKBytes + r0 * Rv + c * 16;
         const bool v_on = c < (Rv >> 4);
         const int s0 = lo + (n >> 1) * kTile + (n & 1) * kHalf + r0;
+        for (int g = 0; g < G; ++g) {
+          const int stage = g * kSlots + pw, hk = (h0 + g) / gqa;
+          if (use > 0) ok = mbar_wait(bar_empty(stage), (use - 1) & 1);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          const uint8_t* kbase = reinterpret_cast<const uint8_t*>(p.latent_k) + (int64_t)hk * p.k_stride_h;
+          const uint8_t* vbase_g = reinterpret_cast<const uint8_t*>(p.latent_v) + (int64_t)hk * p.v_stride_h;
+          const uint32_t dst = sRing + stage * kUnitBytes;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const bool valid = s0 + 8 * k < hi;  // rows past the end are zero-filled
-          const int64_t sl = valid ? page[s0 + 8 * k] : 0;
-          cp_async16(dst + doff_k + k * 512, kbase + c * 16 + sl * p.k_stride_t, valid ? 16u : 0u);
-          if (v_on) cp_async16(dst + doff_v + k * 8 * Rv, vbase_g + c * 16 + sl * p.v_stride_t, valid ? 16u : 0u);
+          for (int k = 0; k < 8; ++k) {
+            const bool valid = s0 + 8 * k < hi;  // rows past the end are zero-filled
+            const int64_t sl = valid ? page[s0 + 8 * k] : 0;
+            cp_async16(dst + doff_k + k * 512, kbase + c * 16 + sl * p.k_stride_t, valid ? 16u : 0u);
+            if (v_on) cp_async16(dst + doff_v + k * 8 * Rv, vbase_g + c * 16 + sl * p.v_stride_t, valid ? 16u : 0u);
+          }
+          cp_async_arrive_noinc(bar_full(stage));
+          __syncwarp();
+          if (lane == 0) publish(stage, use);
         }
-        cp_async_arrive_noinc(bar_full(stage));
       }
-      // Publish "unit n has been requested".  A consumer waits for this before it waits on
-      // the slot's mbarrier: the request is made only after the slot's previous unit was
-      // consumed, so from then on the parity wait cannot be a phase ahead or behind.
-      __syncwarp();
-      if (lane == 0)
-        asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(sbase + kOffIssued + 4u * stage), "r"(use + 1)
-                     : "memory");
-    };
-    // this warp's units: every kProducers-th of the sequence (n, g), g running fastest
-    auto advance = [&](int& n, int& g) {
-      g += kProducers;
-      while (g >= G) {
-        g -= G;
-        ++n;
-      }
-    };
-    int n = 0, g = pw - kProducers;
-    advance(n, g);
-    int e0 = -1, e1 = -1, first = 0;
-    if (n < n_units) fetch_entries(n, e0, e1, first);
-    bool ok = true;
-    while (n < n_units) {
-      int n2 = n, g2 = g;
-      advance(n2, g2);
-      int f0 = -1, f1 = -1, ffirst = 0;
-      if (n2 < n_units) fetch_entries(n2, f0, f1, ffirst);  // the next unit's entries, a unit ahead
-      const int use = n / kSlots, stage = g * kSlots + (n - use * kSlots);
-      if (use > 0) {
-        ok = mbar_wait(bar_empty(stage), (use - 1) & 1);
-        if (!ok) break;
-      }
-      issue_unit(n, g, stage, use, e0, e1, first);
-      n = n2;
-      g = g2;
       e0 = f0;
       e1 = f1;
       first = ffirst;
