@@ -313,6 +313,10 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
   const bool wk_vec = p.wk_dtype == WSVD_F16 && (p.wk_stride_r & 7) == 0 &&
                       (reinterpret_cast<uintptr_t>(p.wk) & 15) == 0;
   uint4 wpre[8];
+  // requested during set-up so that their latency is hidden behind it: the epilogue
+  // lanes' first two page entries and first scales, the producers' first page entries
+  int slot0 = -1, slot_n = -1, pe0 = -1, pe1 = -1, pfirst = 0;
+  unsigned short sk_raw = 0, sv_raw = 0;
 
   // ---- set-up: barriers + tensor memory (MMA warp), scaled q to shared memory (epilogue warps)
   if (warp == kMmaWarp) {
@@ -335,10 +339,24 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
     tmem_relinquish();
     tc_fence_before();
-  } else if (warp < 4 * G) {
-    if (ta.use_tma && warp == 0 && lane == 0) {
+  } else if (warp > kMmaWarp) {
+    if (ta.use_tma && lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&ta.tmap_k)) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&ta.tmap_v)) : "memory");
+    }
+    // page entries of this producer's first unit (same indexing as fetch_entries below)
+    const int n = warp - kMmaWarp - 1;
+    if (n < 2 * ntiles) {
+      const int s0t = lo + (n >> 1) * kTile, sa = s0t + (n & 1) * kHalf + 2 * lane;
+      if (sa < hi) pe0 = page[sa];
+      if (sa + 1 < hi) pe1 = page[sa + 1];
+      pfirst = page[s0t];
+    }
+  } else if (warp < 4 * G) {
+    {
+      const int s_first = lo + (warp & 3) * 32 + lane;
+      if (s_first < hi) slot0 = page[s_first];
+      if (s_first + kTile < hi) slot_n = page[s_first + kTile];
     }
     // the head's slice of wk for the [P;Q] build: requested now, used after the barrier
     if (wk_vec) {
@@ -358,6 +376,11 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       const int g = idx >> 7, d = idx & 127;
       const __half* qp = reinterpret_cast<const __half*>(p.q) + (int64_t)b * p.q_stride_b + (int64_t)(h0 + g) * p.q_stride_h;
       qs[idx] = __half2float(qp[d]) * qscale;
+    }
+    if (slot0 >= 0) {
+      const int hk_pre = (h0 + (warp >> 2)) / gqa;
+      sk_raw = reinterpret_cast<const unsigned short*>(p.k_scale)[(int64_t)hk_pre * p.ks_stride_h + (int64_t)slot0 * p.ks_stride_t];
+      sv_raw = reinterpret_cast<const unsigned short*>(p.v_scale)[(int64_t)hk_pre * p.vs_stride_h + (int64_t)slot0 * p.vs_stride_t];
     }
   }
   __syncthreads();
@@ -440,8 +463,7 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
     auto publish = [&](int stage, int use) {
       asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(sbase + kOffIssued + 4u * stage), "r"(use + 1) : "memory");
     };
-    int e0 = -1, e1 = -1, first = 0;
-    if (pw < n_units) fetch_entries(pw, e0, e1, first);
+    int e0 = pe0, e1 = pe1, first = pfirst;  // unit pw's entries were requested during set-up
     bool ok = true;
     int use = 0;
     for (int n = pw; n < n_units && ok; n += kSlots, ++use) {
@@ -603,14 +625,10 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
     for (int e = 0; e < 8; ++e) acc[e] = 0ull;
     const int rg = lane & 3, tg = lane >> 2;
     const bool pv_on = rg < (Rv >> 4);
-    unsigned short sk_raw, sv_raw, sk_n = 0, sv_n = 0;
+    unsigned short sk_n = 0, sv_n = 0;
     uint4 v_cur[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) v_cur[k] = make_uint4(0u, 0u, 0u, 0u);
-    int slot_n;
-    load_slot(lo + row, slot_n);
-    load_scales(slot_n, sk_raw, sv_raw);
-    load_slot(lo + kTile + row, slot_n);
     bool ok = true;
 
     for (int t = 0; t < ntiles; ++t) {
