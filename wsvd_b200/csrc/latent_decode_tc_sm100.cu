@@ -192,6 +192,12 @@ __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void named_barrier(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
+// warp-wide maximum in one instruction (sm_100a)
+__device__ __forceinline__ float warp_max_redux(float v) {
+  float r;
+  asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+  return r;
+}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -709,7 +715,7 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       const float z = valid ? (d0 + d1) * sk : -INFINITY;
 
       // ---- online softmax, per warp
-      const float tmax = warp_max(z);
+      const float tmax = warp_max_redux(z);
       if (tmax > m_w) {
         const float sc = fast_exp2(m_w - tmax);  // m_w = -inf -> 0
         const uint64_t sc2 = pk(sc, sc);
