@@ -18,14 +18,18 @@
 // shared memory) in fp32.  P.V runs on the CUDA cores in fp32 from the int8 V rows.
 // Nothing is rounded to f16 except the two GEMM operands.
 //
-// CTA = one (split, group of 4 heads, sequence); 18 warps:
-//   warps 0-15  epilogue, 4 per head: warp w owns tensor-memory lanes 32*(w%4)..+31
-//   warp 16     producer of the K and V rows: every head has a ring of three 8 KB slots of
-//               half a tile (64 tokens); two TMA tensor copies per slot when the tile's
-//               token slots are consecutive, else a gather of rows with 16-byte cp.async
-//               through the page table.  A slot is handed back as soon as the score is
-//               computed (the V rows are copied to registers first).
-//   warp 17     one thread issues the table tile loads (cp.async.bulk) and the MMAs
+// CTA = one (split, group of 4 heads, sequence); 20 warps:
+//   warps 0-15   epilogue, 4 per head: warp w owns tensor-memory lanes 32*(w%4)..+31.  A warp
+//                copies its 32 K rows and its V rows from the ring slot to registers as soon as
+//                they have landed and hands the slot back before any arithmetic.
+//   warp 16      one thread issues the table tile loads (cp.async.bulk) and the MMAs
+//   warps 17-19  request the K and V rows: every head has a ring of three 8 KB slots of half a
+//                tile (64 tokens), producer warp p owns slot p of every head; two TMA tensor
+//                copies per slot when the half-tile's token slots are consecutive (lane g
+//                serves head g on its own), else a gather of rows with 16-byte cp.async
+//                through the page table.
+// More than 16 warps cap the kernel at 96 registers per thread; the four non-epilogue warps
+// fill exactly one warp slot per scheduler.
 // Every wait on an mbarrier is bounded; on a time-out the kernel records a status code
 // and every role falls through to the common exit, which frees the tensor memory.
 #include <cuda.h>
@@ -50,6 +54,7 @@ constexpr int kThreads = (kEpiWarps + 1 + kProducers) * 32;
 constexpr int kHalf = kTile / 2;
 constexpr int kSlots = 3;
 constexpr int kStages = kG * kSlots;
+static_assert(kProducers == kSlots, "producer warp p owns ring slot p of every head");
 constexpr uint32_t kKBytes = kHalf * 64;            // K rows of one half-tile
 constexpr uint32_t kUnitBytes = 2 * kKBytes;        // + V rows
 constexpr uint32_t kAHalfBytes = kTile * 128;       // 128 rows x 64 f16
