@@ -40,7 +40,7 @@ typedef enum WsvdStatus {
   WSVD_ERR_TOO_LARGE = 8         /* size beyond a documented fixed limit */
 } WsvdStatus;
 
-typedef enum WsvdDtype { WSVD_I8 = 0, WSVD_F16 = 1 } WsvdDtype;
+typedef enum WsvdDtype { WSVD_I8 = 0, WSVD_F16 = 1, WSVD_F32 = 2 /* quant-append input only */ } WsvdDtype;
 typedef enum WsvdRopeLayout { WSVD_ROPE_HALF = 0, WSVD_ROPE_INTERLEAVED = 1 } WsvdRopeLayout;
 
 /* Which stage-1 kernel to run.  AUTO picks the tcgen05 kernel when the shape allows. */
@@ -103,8 +103,10 @@ int wsvd_rope_table_init(void* table, size_t table_bytes, int32_t positions, int
                          void* stream);
 
 /*
- * Device-side status of the tensor-core kernel: 0, or the code of the first bounded wait
- * that timed out (1 producer, 2 MMA issuer, 3 epilogue).  SYNCHRONISES the device; meant
+ * Device-side status of the kernels: 0, or the highest code recorded since the last reset:
+ * 1-3 a bounded wait of the tensor-core kernel timed out (1 copy issuer, 2 MMA issuer,
+ * 3 epilogue), 4 its shared-memory base was misaligned, 5 wsvd_latent_quant_append_i8 met
+ * a position outside [0, max_len) and skipped that row.  SYNCHRONISES the device; meant
  * for tests and diagnostics.  wsvd_kernel_status_reset clears it.
  */
 int wsvd_kernel_status(uint32_t* status);
@@ -174,6 +176,35 @@ typedef struct WsvdDenseDecodeParams {
 } WsvdDenseDecodeParams;
 size_t wsvd_dense_decode_workspace_bytes(const WsvdDenseDecodeParams* p);
 int wsvd_dense_decode_f16(const WsvdDenseDecodeParams* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Decode-step producer of the latent cache: quantise the new token's K and V latents
+ * x_k [B, Hkv, Rk], x_v [B, Hkv, Rv] (f16 or f32, innermost stride 1) per (sequence, head)
+ * to int8 with an f16 scale, and store them at token slot
+ * req_to_token[b_req_idx[b]][b_seq_len[b]], i.e. b_seq_len holds the lengths BEFORE the
+ * append and the caller increments it afterwards.  Quantiser: scale = max|x| / 127 (1 for
+ * an all-zero row) stored as f16, q = clamp(round_half_even(x / f16(scale)), -128, 127)
+ * (fake_quant/quant_utils.py:30-33,175-184).  The reference has no such kernel: its layer
+ * wrapper computes the new latents and drops them (efficiency/layer_utils.py:319-321) and
+ * its test script fills the caches with torch ops (efficiency/test_timing_layer.py:267-275).
+ * A sequence whose position is outside [0, max_len) is skipped and status 5 is recorded
+ * (wsvd_kernel_status).  rank_k, rank_v <= 128.
+ */
+typedef struct WsvdQuantAppendParams {
+  const void* x_k;          int64_t xk_stride_b, xk_stride_h;
+  const void* x_v;          int64_t xv_stride_b, xv_stride_h;
+  void* latent_k;           int64_t k_stride_t, k_stride_h;     /* int8 [T, Hkv, Rk] */
+  void* k_scale;            int64_t ks_stride_t, ks_stride_h;   /* f16  [T, Hkv] */
+  void* latent_v;           int64_t v_stride_t, v_stride_h;
+  void* v_scale;            int64_t vs_stride_t, vs_stride_h;
+  const int32_t* req_to_token; int64_t rtt_stride;
+  const int32_t* b_req_idx;
+  const int32_t* b_seq_len;
+  int32_t batch, n_kv_heads, rank_k, rank_v;
+  int32_t max_len;          /* columns of req_to_token */
+  int32_t x_dtype;          /* WSVD_F16 or WSVD_F32 */
+} WsvdQuantAppendParams;
+int wsvd_latent_quant_append_i8(const WsvdQuantAppendParams* p, void* stream);
 
 /*
  * The whole op for callers that cannot supply a workspace.  No counterpart in the

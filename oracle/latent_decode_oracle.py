@@ -87,6 +87,29 @@ def quantize_per_token(x: torch.Tensor, bits: int = 8) -> Tuple[torch.Tensor, to
     return q.to(torch.int8), scale_h
 
 
+
+def quant_append_oracle(x_k, x_v, b_seq_len, b_req_idx, req_to_token, latent_k, k_scale, latent_v, v_scale):
+    """Append one token per sequence to the latent cache (in place, CPU tensors).
+
+    x_k [B, Hkv, Rk], x_v [B, Hkv, Rv] are quantised with `quantize_per_token`
+    (fake_quant/quant_utils.py:30-33,175-184) and stored at token slot
+    req_to_token[b_req_idx[b], b_seq_len[b]].  The reference drops the new latents
+    (efficiency/layer_utils.py:319-321); this states what a cache producer with its
+    quantiser has to write.  Sequences whose position has no page-table column are skipped.
+    """
+    qk, sk = quantize_per_token(x_k)
+    qv, sv = quantize_per_token(x_v)
+    for b in range(x_k.shape[0]):
+        pos = int(b_seq_len[b])
+        if pos < 0 or pos >= req_to_token.shape[1]:
+            continue
+        slot = int(req_to_token[int(b_req_idx[b]), pos])
+        latent_k[slot] = qk[b]
+        k_scale[slot] = sk[b]
+        latent_v[slot] = qv[b]
+        v_scale[slot] = sv[b]
+
+
 def _rope_half(k: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
     """Half-split (NeoX/HF) pairing (i, i+D/2), the kernel's convention
     (stage1.py:65-66,165-166).  k: [S, H, D]; pos: [S]."""

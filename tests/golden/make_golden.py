@@ -21,6 +21,13 @@ Two kinds of vectors are written (numpy .npz, small):
   with (other choices make stage 2 read unwritten partials); (3) workspaces are
   allocated on the CPU.  These vectors pin the kernel's half-split RoPE pairing,
   its position convention, the split-KV partial format and the stage-2 merge.
+
+* quant_ref_sym_int8.npz — `sym_quant` (fake_quant/quant_utils.py:30-33) applied with the
+  per-token scale of `ActQuantizer.find_params_per_token_groupwise`
+  (fake_quant/quant_utils.py:175-184: scale = amax/maxq, 1 for an all-zero row).  It pins
+  the rounding and clamp of the latent quantiser that the append kernel restates.
+  `quant_utils` imports three modules that the quantiser itself never touches (`utils`,
+  `hadamard_utils`, `fast_hadamard_transform`); empty stand-ins are registered for them.
 """
 import os
 import sys
@@ -205,9 +212,37 @@ def make_triton(ref_root):
     print("triton_dense_gqa_ragged_paged: out", tuple(out.shape), float(out.float().abs().max()))
 
 
+def make_quant(ref_root):
+    import types
+
+    for name in ("utils", "hadamard_utils", "fast_hadamard_transform"):
+        sys.modules.setdefault(name, types.ModuleType(name))
+    sys.path.insert(0, os.path.join(ref_root, "fake_quant"))
+    import quant_utils as qu
+
+    gen = torch.Generator().manual_seed(77)
+    x = torch.randn(6, 5, 64, generator=gen) * torch.rand(6, 5, 1, generator=gen) * 3.0
+    x[1, 2] = 0.0                      # an all-zero row: scale 1
+    x[2, 3, 7] = x[2, 3].abs().max() * -1.0001  # the extreme is negative
+    x[3, 1] = torch.round(x[3, 1] * 4) / 8      # many exact .5 ties after scaling
+    _, maxq = qu.get_minq_maxq(8, True)
+    amax = x.abs().amax(dim=-1, keepdim=True)
+    scale = amax / maxq
+    scale[amax == 0] = 1
+    # the cache stores the scale as f16; quantise against the stored value
+    scale_h = scale.to(torch.float16)
+    q, _ = qu.sym_quant(x, scale_h.float(), maxq)
+    np.savez_compressed(
+        os.path.join(HERE, "quant_ref_sym_int8.npz"),
+        x=x.numpy(), scale=scale_h.squeeze(-1).numpy(), q=q.to(torch.int8).numpy(),
+    )
+    print("quant_ref_sym_int8: q range", int(q.min()), int(q.max()))
+
+
 if __name__ == "__main__":
     if len(sys.argv) != 2:
         sys.exit("usage: make_golden.py <path to the WSVD checkout>")
     root = sys.argv[1]
     make_torch_ref(root)
     make_triton(root)
+    make_quant(root)

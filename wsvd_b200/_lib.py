@@ -106,6 +106,23 @@ class DenseDecodeParams(ctypes.Structure):
     ]
 
 
+class QuantAppendParams(ctypes.Structure):
+    """ctypes mirror of WsvdQuantAppendParams."""
+
+    _fields_ = [
+        ("x_k", ctypes.c_void_p), ("xk_stride_b", ctypes.c_int64), ("xk_stride_h", ctypes.c_int64),
+        ("x_v", ctypes.c_void_p), ("xv_stride_b", ctypes.c_int64), ("xv_stride_h", ctypes.c_int64),
+        ("latent_k", ctypes.c_void_p), ("k_stride_t", ctypes.c_int64), ("k_stride_h", ctypes.c_int64),
+        ("k_scale", ctypes.c_void_p), ("ks_stride_t", ctypes.c_int64), ("ks_stride_h", ctypes.c_int64),
+        ("latent_v", ctypes.c_void_p), ("v_stride_t", ctypes.c_int64), ("v_stride_h", ctypes.c_int64),
+        ("v_scale", ctypes.c_void_p), ("vs_stride_t", ctypes.c_int64), ("vs_stride_h", ctypes.c_int64),
+        ("req_to_token", ctypes.c_void_p), ("rtt_stride", ctypes.c_int64),
+        ("b_req_idx", ctypes.c_void_p), ("b_seq_len", ctypes.c_void_p),
+        ("batch", ctypes.c_int32), ("n_kv_heads", ctypes.c_int32), ("rank_k", ctypes.c_int32),
+        ("rank_v", ctypes.c_int32), ("max_len", ctypes.c_int32), ("x_dtype", ctypes.c_int32),
+    ]
+
+
 # name -> (restype, argtypes); every symbol include/wsvd_b200.h declares
 _P = ctypes.POINTER(LatentDecodeParams)
 SYMBOLS = {
@@ -124,6 +141,7 @@ SYMBOLS = {
     "wsvd_dense_decode_f16": (ctypes.c_int, [ctypes.POINTER(DenseDecodeParams), ctypes.c_void_p, ctypes.c_size_t,
                                              ctypes.c_void_p]),
     "wsvd_latent_decode_static": (ctypes.c_int, [_P, ctypes.c_void_p]),
+    "wsvd_latent_quant_append_i8": (ctypes.c_int, [ctypes.POINTER(QuantAppendParams), ctypes.c_void_p]),
     "wsvd_latent_decode_stage1": (ctypes.c_int, [_P, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p]),
     "wsvd_decode_stage2": (ctypes.c_int, [
         ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,

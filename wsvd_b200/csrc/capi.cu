@@ -198,14 +198,30 @@ int wsvd_rope_table_init(void* table, size_t table_bytes, int32_t positions, int
 
 int wsvd_kernel_status(uint32_t* status) {
   if (!status) return WSVD_ERR_NULL_POINTER;
-  unsigned int v = 0;
+  unsigned int v = 0, w = 0;
   cudaError_t e = wsvd::read_tc_status(&v);
-  *status = v;
+  if (e == cudaSuccess) e = wsvd::read_append_status(&w);
+  *status = v > w ? v : w;
   return e == cudaSuccess ? WSVD_OK : cuda_fail(e);
 }
 
 int wsvd_kernel_status_reset(void) {
   cudaError_t e = wsvd::reset_tc_status();
+  if (e == cudaSuccess) e = wsvd::reset_append_status();
+  return e == cudaSuccess ? WSVD_OK : cuda_fail(e);
+}
+
+int wsvd_latent_quant_append_i8(const WsvdQuantAppendParams* p, void* stream) {
+  if (!p) return WSVD_ERR_NULL_POINTER;
+  if (p->batch < 0 || p->n_kv_heads <= 0 || p->max_len < 0) return WSVD_ERR_BAD_SHAPE;
+  if (p->rank_k <= 0 || p->rank_k > 128 || p->rank_v <= 0 || p->rank_v > 128) return WSVD_ERR_BAD_SHAPE;
+  if (p->x_dtype != WSVD_F16 && p->x_dtype != WSVD_F32) return WSVD_ERR_BAD_DTYPE;
+  if (p->batch == 0) return WSVD_OK;
+  if (!p->x_k || !p->x_v || !p->latent_k || !p->latent_v || !p->k_scale || !p->v_scale || !p->req_to_token ||
+      !p->b_req_idx || !p->b_seq_len)
+    return WSVD_ERR_NULL_POINTER;
+  if ((int64_t)p->batch * p->n_kv_heads > (int64_t)1 << 28) return WSVD_ERR_TOO_LARGE;
+  cudaError_t e = wsvd::launch_quant_append(*p, reinterpret_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? WSVD_OK : cuda_fail(e);
 }
 

@@ -303,3 +303,51 @@ def dense_decode(q, infer_state, cache_k, cache_v, out=None, alloc_tensor_func: 
         check(_lib.lib().wsvd_dense_decode_f16(ctypes.byref(p), _ptr(workspace), have, _stream(stream)),
               "wsvd_dense_decode_f16")
     return out
+
+
+def latent_quant_append(x_k, x_v, infer_state, cache_latent_k, cache_latent_k_scale, cache_latent_v,
+                        cache_latent_v_scale, stream=None):
+    """Quantise the new token's latents and store them in the cache (in place).
+
+    x_k [B, Hkv, Rk], x_v [B, Hkv, Rv] (f16 or f32) are written, as int8 with one f16 scale
+    per (sequence, head), to token slot ``req_to_token_indexs[b_req_idx[b], b_seq_len[b]]``:
+    ``infer_state.b_seq_len`` holds the lengths before the append, the caller increments it
+    afterwards.  Quantiser: fake_quant/quant_utils.py:30-33,175-184 against the stored f16
+    scale.  The reference has no counterpart (efficiency/layer_utils.py:319-321 drops the
+    new latents)."""
+    from ._lib import QuantAppendParams
+
+    _cuda_tensor("x_k", x_k, (torch.float16, torch.float32), 3)
+    _cuda_tensor("x_v", x_v, (torch.float16, torch.float32), 3)
+    _need(x_k.dtype == x_v.dtype, "x_k and x_v must share a dtype", TypeError)
+    B, Hkv, Rk = x_k.shape
+    Rv = x_v.shape[2]
+    _need(x_v.shape[:2] == (B, Hkv), "x_k and x_v disagree on batch or heads")
+    _cuda_tensor("cache_latent_k", cache_latent_k, (torch.int8,), 3)
+    _cuda_tensor("cache_latent_v", cache_latent_v, (torch.int8,), 3)
+    _cuda_tensor("cache_latent_k_scale", cache_latent_k_scale, (torch.float16,), 2, inner_contiguous=False)
+    _cuda_tensor("cache_latent_v_scale", cache_latent_v_scale, (torch.float16,), 2, inner_contiguous=False)
+    _need(cache_latent_k.shape[1:] == (Hkv, Rk) and cache_latent_v.shape[1:] == (Hkv, Rv),
+          "cache shapes must be [T, Hkv, Rk] and [T, Hkv, Rv]")
+    _need(0 < Rk <= 128 and 0 < Rv <= 128, "ranks must be in 1..128")
+    rtt = infer_state.req_manager.req_to_token_indexs
+    _cuda_tensor("b_seq_len", infer_state.b_seq_len, (torch.int32,), 1)
+    _cuda_tensor("b_req_idx", infer_state.b_req_idx, (torch.int32,), 1)
+    _cuda_tensor("req_to_token_indexs", rtt, (torch.int32,), 2)
+    _need(infer_state.b_seq_len.numel() == B and infer_state.b_req_idx.numel() == B, "batch metadata must have B entries")
+    p = QuantAppendParams()
+    p.x_k, p.xk_stride_b, p.xk_stride_h = x_k.data_ptr(), x_k.stride(0), x_k.stride(1)
+    p.x_v, p.xv_stride_b, p.xv_stride_h = x_v.data_ptr(), x_v.stride(0), x_v.stride(1)
+    p.latent_k, p.k_stride_t, p.k_stride_h = cache_latent_k.data_ptr(), cache_latent_k.stride(0), cache_latent_k.stride(1)
+    p.latent_v, p.v_stride_t, p.v_stride_h = cache_latent_v.data_ptr(), cache_latent_v.stride(0), cache_latent_v.stride(1)
+    p.k_scale, p.ks_stride_t, p.ks_stride_h = (cache_latent_k_scale.data_ptr(), cache_latent_k_scale.stride(0),
+                                               cache_latent_k_scale.stride(1))
+    p.v_scale, p.vs_stride_t, p.vs_stride_h = (cache_latent_v_scale.data_ptr(), cache_latent_v_scale.stride(0),
+                                               cache_latent_v_scale.stride(1))
+    p.req_to_token, p.rtt_stride = rtt.data_ptr(), rtt.stride(0)
+    p.b_req_idx, p.b_seq_len = infer_state.b_req_idx.data_ptr(), infer_state.b_seq_len.data_ptr()
+    p.batch, p.n_kv_heads, p.rank_k, p.rank_v = B, Hkv, Rk, Rv
+    p.max_len = rtt.shape[1]
+    p.x_dtype = 1 if x_k.dtype == torch.float16 else 2
+    with torch.cuda.device(x_k.device):
+        check(_lib.lib().wsvd_latent_quant_append_i8(ctypes.byref(p), _stream(stream)), "wsvd_latent_quant_append_i8")
