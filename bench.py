@@ -10,7 +10,8 @@ batch of one decoder layer.  Rank 0 prints ONE JSON line.
   context 8192), inputs resident in HBM and larger than L2.
 * N > 1 (launched under torchrun, one rank per GPU): every rank owns a head shard of
   that same shape (weak scaling: 40 local heads per GPU) and the step ends with the
-  path's one exchange, an NCCL all-gather of the [B, H_local, 128] outputs.
+  path's one exchange, the all-gather of the [B, H_local, 128] outputs, fused into the
+  merge kernel as peer stores (--collective nccl: the library all-gather instead).
 * `value` = algorithmic latent+scale bytes of all ranks / max-over-ranks device time.
 * `e2e` = the same step through the public Python op with the per-step inputs (q and
   the batch metadata) copied from pinned host memory and the result copied back to the
@@ -159,6 +160,8 @@ def main():
     ap.add_argument("--kernel", default="auto", choices=["auto", "generic", "tc"])
     ap.add_argument("--split-len", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--collective", default="fused", choices=["fused", "nccl"],
+                    help="N>1: head all-gather fused into the merge kernel (peer stores), or an NCCL all_gather")
     ap.add_argument("--no-dense", action="store_true", help="skip the dense f16 baseline kernel timing")
     args = ap.parse_args()
 
@@ -207,7 +210,33 @@ def main():
     stream = torch.cuda.current_stream()
     lib = _lib.lib()
 
+    # N>1: the path's one exchange, the all-gather of the heads.  "fused": the merge kernel of
+    # every rank stores its rows into all ranks' gathered buffers and runs the group barrier
+    # (wsvd_latent_decode_gather); "nccl": the plain library collective after the op.
+    pg, collective = None, "none"
+    if world > 1:
+        collective = "nccl all_gather of [B,H_local,128] f16"
+        if args.collective == "fused":
+            from wsvd_b200.dist import PeerGather
+            ok = torch.ones(1, device=dev)
+            try:
+                pg = PeerGather(B, H * world, D, device=dev, timeout_ms=10000)
+            except Exception as exc:  # no peer mapping on this box: say so and use the library collective
+                print(f"[bench] rank {rank}: peer buffers unavailable ({exc}); using NCCL", file=sys.stderr)
+                ok.zero_()
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if ok.item() == 0:
+                pg = None
+            else:
+                collective = "fused into the merge kernel: peer stores of [B,H_local,128] f16 + flag barrier"
+
     def step():
+        if pg is not None:
+            ps, _parity = pg.peer_set()
+            _lib.check(lib.wsvd_latent_decode_gather(ctypes.byref(p), ctypes.byref(ps), ctypes.c_void_p(ws.data_ptr()),
+                                                     ws.numel() * 4, ctypes.c_void_p(stream.cuda_stream)),
+                       "wsvd_latent_decode_gather")
+            return
         _lib.check(lib.wsvd_latent_decode(ctypes.byref(p), ctypes.c_void_p(ws.data_ptr()), ws.numel() * 4,
                                           ctypes.c_void_p(stream.cuda_stream)), "wsvd_latent_decode")
         if world > 1:
@@ -287,10 +316,15 @@ def main():
         q_dev.copy_(q_host, non_blocking=True)
         len_dev.copy_(len_host, non_blocking=True)
         req_dev.copy_(req_host, non_blocking=True)
-        o = op(q_dev, st2, H, D, case.latent_k, case.k_scale, case.latent_v, case.v_scale, case.wk, None,
-               wv=case.wv, out=out, workspace=ws, split_len=args.split_len, kernel=args.kernel)
-        if world > 1:
-            dist.all_gather_into_tensor(gathered, o)
+        if pg is not None:
+            o = pg.decode(q_dev, st2, case.latent_k, case.k_scale, case.latent_v, case.v_scale, case.wk, None,
+                          wv=case.wv, workspace=ws, split_len=args.split_len, kernel=args.kernel)
+            o = o[:, rank * H:(rank + 1) * H]  # the caller of this rank reads its heads back
+        else:
+            o = op(q_dev, st2, H, D, case.latent_k, case.k_scale, case.latent_v, case.v_scale, case.wk, None,
+                   wv=case.wv, out=out, workspace=ws, split_len=args.split_len, kernel=args.kernel)
+            if world > 1:
+                dist.all_gather_into_tensor(gathered, o)
         out_host.copy_(o, non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the caller consumes the host result every step
 
@@ -298,6 +332,9 @@ def main():
         e2e_step()
     ms_e2e = timed(e2e_step, args.steps) / args.steps
     clocks = sampler.stop() if rank == 0 else None
+    status = torch.tensor([ops.kernel_status()], device=dev)
+    if world > 1:
+        dist.all_reduce(status, op=dist.ReduceOp.MAX)
     h2d = q_host.numel() * 2 + len_host.numel() * 4 + req_host.numel() * 4
     d2h = out_host.numel() * 2
 
@@ -313,7 +350,7 @@ def main():
                 "workload": spec.name, "batch": spec.batch, "heads_per_gpu": H, "head_dim": D,
                 "rank_k": spec.rank_k, "rank_v": spec.rank_v, "context": spec.max_len, "split_len": split_len,
                 "n_splits": n_splits, "kernel": args.kernel, "parallelism": f"heads x{world}",
-                "collective": "nccl all_gather of [B,H_local,128] f16" if world > 1 else "none",
+                "collective": collective,
                 "l2": (f"inputs {bytes_rank / 1e6:.0f} MB per GPU, larger than the 126 MB L2" if flush is None else
                        f"inputs {bytes_rank / 1e6:.0f} MB per GPU fit L2: a 512 MB buffer is written before every "
                        "timed call"),
@@ -327,7 +364,7 @@ def main():
             "e2e": {"value": bytes_total / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "us_per_layer": ms_e2e * 1e3,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": args.steps * 2,
-            "kernel_status": ops.kernel_status(),
+            "kernel_status": int(status.item()),
             "clocks": clocks,
         }
         if world == 1 and not args.no_dense:
@@ -358,6 +395,8 @@ def main():
             line["cpu_baseline"]["us_per_layer_extrapolated"] = cb["us_per_layer_extrapolated"]
         print(json.dumps(line), flush=True)
     if world > 1:
+        if pg is not None:
+            pg.close()
         dist.barrier()
         dist.destroy_process_group()
 

@@ -106,7 +106,8 @@ int wsvd_rope_table_init(void* table, size_t table_bytes, int32_t positions, int
  * Device-side status of the kernels: 0, or the highest code recorded since the last reset:
  * 1-3 a bounded wait of the tensor-core kernel timed out (1 copy issuer, 2 MMA issuer,
  * 3 epilogue), 4 its shared-memory base was misaligned, 5 wsvd_latent_quant_append_i8 met
- * a position outside [0, max_len) and skipped that row.  SYNCHRONISES the device; meant
+ * a position outside [0, max_len) and skipped that row, 6 the group barrier of
+ * wsvd_latent_decode_gather gave up waiting for a peer.  SYNCHRONISES the device; meant
  * for tests and diagnostics.  wsvd_kernel_status_reset clears it.
  */
 int wsvd_kernel_status(uint32_t* status);
@@ -205,6 +206,59 @@ typedef struct WsvdQuantAppendParams {
   int32_t x_dtype;          /* WSVD_F16 or WSVD_F32 */
 } WsvdQuantAppendParams;
 int wsvd_latent_quant_append_i8(const WsvdQuantAppendParams* p, void* stream);
+
+/*
+ * Head-sharded multi-GPU decode with the all-gather fused into the merge kernel.
+ *
+ * The op shards by attention head with no exchange between heads
+ * (flash_int8_latent_per_head_decoding_rope_stage1.py:60, program_id(1) = head); the one
+ * exchange of the path is the all-gather of the [B, H/g, D] outputs.  The reference is
+ * single-GPU and has no counterpart.  Here every rank's merge kernel stores its rows
+ * straight into the gathered [B, H_total, D] f16 buffer of EVERY rank (plain peer stores,
+ * no multicast), and its last block runs the group barrier: a system-scope fence, one flag
+ * store per peer and a bounded wait for the peers' flags.  When the call's kernels have
+ * finished on every rank, every rank's buffer holds all heads.
+ *
+ *  - out[i], flags[i]: rank i's gathered buffer and flag array (WSVD_MAX_PEERS uint32,
+ *    zero before the first call) as mapped in THIS process; entry `rank` is local memory.
+ *    counter: one local uint32, zero before the first call.
+ *  - epoch: the same value on all ranks for a given step, never 0, +1 per step.
+ *  - Every rank must make the call with the same batch; p->out is ignored; p->n_q_heads is
+ *    the LOCAL head count and head_offset the first global head of the shard.
+ *  - Reuse: a rank may overwrite a peer's buffer for step e+1 while that peer still reads
+ *    step e.  Alternate between two buffers by epoch parity and consume a buffer on the
+ *    stream that makes the next call: a peer passes the barrier of step e+1 only after this
+ *    rank has enqueued step e+1 behind its readers of step e.
+ *  - A wait that runs out (timeout_ms, 0 = 2000) records status 6 and the kernel returns;
+ *    the context stays usable.
+ */
+#define WSVD_MAX_PEERS 8
+typedef struct WsvdPeerSet {
+  void* out[WSVD_MAX_PEERS];
+  uint32_t* flags[WSVD_MAX_PEERS];
+  uint32_t* counter;
+  int32_t n_peers, rank;
+  int32_t head_offset;
+  uint32_t epoch;
+  int64_t out_stride_b, out_stride_h;  /* of the gathered buffers, in f16 elements */
+  int32_t timeout_ms;
+} WsvdPeerSet;
+int wsvd_latent_decode_gather(const WsvdLatentDecodeParams* p, const WsvdPeerSet* peers, void* workspace,
+                              size_t workspace_bytes, void* stream);
+
+/*
+ * Device memory that the other ranks of a node can map (CUDA IPC), for the buffers of
+ * WsvdPeerSet.  wsvd_peer_alloc returns zeroed memory from cudaMalloc (these calls are the
+ * only ones in the library that allocate, and they synchronise); wsvd_peer_export writes
+ * the 64-byte handle to send to the peers; wsvd_peer_import maps a peer's handle and
+ * enables peer access; wsvd_peer_release unmaps it.
+ */
+#define WSVD_PEER_HANDLE_BYTES 64
+int wsvd_peer_alloc(size_t bytes, void** ptr);
+int wsvd_peer_free(void* ptr);
+int wsvd_peer_export(void* ptr, unsigned char handle[WSVD_PEER_HANDLE_BYTES]);
+int wsvd_peer_import(const unsigned char handle[WSVD_PEER_HANDLE_BYTES], void** ptr);
+int wsvd_peer_release(void* ptr);
 
 /*
  * The whole op for callers that cannot supply a workspace.  No counterpart in the

@@ -123,6 +123,21 @@ class QuantAppendParams(ctypes.Structure):
     ]
 
 
+MAX_PEERS = 8
+PEER_HANDLE_BYTES = 64
+
+
+class PeerSet(ctypes.Structure):
+    """ctypes mirror of WsvdPeerSet."""
+
+    _fields_ = [
+        ("out", ctypes.c_void_p * MAX_PEERS), ("flags", ctypes.c_void_p * MAX_PEERS), ("counter", ctypes.c_void_p),
+        ("n_peers", ctypes.c_int32), ("rank", ctypes.c_int32), ("head_offset", ctypes.c_int32),
+        ("epoch", ctypes.c_uint32), ("out_stride_b", ctypes.c_int64), ("out_stride_h", ctypes.c_int64),
+        ("timeout_ms", ctypes.c_int32),
+    ]
+
+
 # name -> (restype, argtypes); every symbol include/wsvd_b200.h declares
 _P = ctypes.POINTER(LatentDecodeParams)
 SYMBOLS = {
@@ -141,6 +156,13 @@ SYMBOLS = {
     "wsvd_dense_decode_f16": (ctypes.c_int, [ctypes.POINTER(DenseDecodeParams), ctypes.c_void_p, ctypes.c_size_t,
                                              ctypes.c_void_p]),
     "wsvd_latent_decode_static": (ctypes.c_int, [_P, ctypes.c_void_p]),
+    "wsvd_latent_decode_gather": (ctypes.c_int, [_P, ctypes.POINTER(PeerSet), ctypes.c_void_p, ctypes.c_size_t,
+                                                 ctypes.c_void_p]),
+    "wsvd_peer_alloc": (ctypes.c_int, [ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p)]),
+    "wsvd_peer_free": (ctypes.c_int, [ctypes.c_void_p]),
+    "wsvd_peer_export": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_char_p]),
+    "wsvd_peer_import": (ctypes.c_int, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]),
+    "wsvd_peer_release": (ctypes.c_int, [ctypes.c_void_p]),
     "wsvd_latent_quant_append_i8": (ctypes.c_int, [ctypes.POINTER(QuantAppendParams), ctypes.c_void_p]),
     "wsvd_latent_decode_stage1": (ctypes.c_int, [_P, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p]),
     "wsvd_decode_stage2": (ctypes.c_int, [

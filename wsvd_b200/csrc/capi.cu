@@ -1,6 +1,7 @@
 // extern "C" entry points: validation, split plan, launches.  No allocation, no
 // synchronisation; everything is enqueued on the caller's stream.
 #include <math.h>
+#include <string.h>
 
 #include "common.cuh"
 
@@ -198,16 +199,19 @@ int wsvd_rope_table_init(void* table, size_t table_bytes, int32_t positions, int
 
 int wsvd_kernel_status(uint32_t* status) {
   if (!status) return WSVD_ERR_NULL_POINTER;
-  unsigned int v = 0, w = 0;
+  unsigned int v = 0, w = 0, x = 0;
   cudaError_t e = wsvd::read_tc_status(&v);
   if (e == cudaSuccess) e = wsvd::read_append_status(&w);
+  if (e == cudaSuccess) e = wsvd::read_peer_status(&x);
   *status = v > w ? v : w;
+  if (x > *status) *status = x;
   return e == cudaSuccess ? WSVD_OK : cuda_fail(e);
 }
 
 int wsvd_kernel_status_reset(void) {
   cudaError_t e = wsvd::reset_tc_status();
   if (e == cudaSuccess) e = wsvd::reset_append_status();
+  if (e == cudaSuccess) e = wsvd::reset_peer_status();
   return e == cudaSuccess ? WSVD_OK : cuda_fail(e);
 }
 
@@ -225,8 +229,9 @@ int wsvd_latent_quant_append_i8(const WsvdQuantAppendParams* p, void* stream) {
   return e == cudaSuccess ? WSVD_OK : cuda_fail(e);
 }
 
-int wsvd_latent_decode(const WsvdLatentDecodeParams* p, void* workspace, size_t workspace_bytes, void* stream) {
-  int st = validate(p, true);
+static int decode_impl(const WsvdLatentDecodeParams* p, const WsvdPeerSet* peers, void* workspace,
+                       size_t workspace_bytes, void* stream) {
+  int st = validate(p, peers == nullptr);
   if (st != WSVD_OK) return st;
   if (p->batch == 0) return WSVD_OK;
   const size_t need = wsvd_latent_decode_workspace_bytes(p);
@@ -244,9 +249,60 @@ int wsvd_latent_decode(const WsvdLatentDecodeParams* p, void* workspace, size_t 
   void* scratch_table = p->rope_table ? nullptr : reinterpret_cast<uint8_t*>(workspace) + partial_bytes(p, ns);
   st = run_stage1(a, scratch_table, s);
   if (st != WSVD_OK) return st;
-  cudaError_t e = wsvd::launch_stage2(mid_o, lse, p->b_seq_len, p->out, p->out_stride_b, p->out_stride_h, p->batch,
-                                      p->n_q_heads, ns, p->rank_v, sl, p->wv, p->wv_stride_r, p->n_kv_heads,
-                                      p->head_dim, s);
+  cudaError_t e =
+      peers ? wsvd::launch_stage2_peers(mid_o, lse, p->b_seq_len, *peers, p->batch, p->n_q_heads, ns, p->rank_v, sl,
+                                        p->wv, p->wv_stride_r, p->n_kv_heads, p->head_dim, s)
+            : wsvd::launch_stage2(mid_o, lse, p->b_seq_len, p->out, p->out_stride_b, p->out_stride_h, p->batch,
+                                  p->n_q_heads, ns, p->rank_v, sl, p->wv, p->wv_stride_r, p->n_kv_heads,
+                                  p->head_dim, s);
+  return e == cudaSuccess ? WSVD_OK : cuda_fail(e);
+}
+
+int wsvd_latent_decode(const WsvdLatentDecodeParams* p, void* workspace, size_t workspace_bytes, void* stream) {
+  return decode_impl(p, nullptr, workspace, workspace_bytes, stream);
+}
+
+int wsvd_latent_decode_gather(const WsvdLatentDecodeParams* p, const WsvdPeerSet* peers, void* workspace,
+                              size_t workspace_bytes, void* stream) {
+  if (!peers) return WSVD_ERR_NULL_POINTER;
+  if (peers->n_peers < 1 || peers->n_peers > WSVD_MAX_PEERS || peers->rank < 0 || peers->rank >= peers->n_peers)
+    return WSVD_ERR_BAD_SHAPE;
+  if (peers->epoch == 0 || peers->head_offset < 0 || peers->timeout_ms < 0) return WSVD_ERR_BAD_SHAPE;
+  if (!peers->counter) return WSVD_ERR_NULL_POINTER;
+  for (int i = 0; i < peers->n_peers; ++i)
+    if (!peers->out[i] || !peers->flags[i]) return WSVD_ERR_NULL_POINTER;
+  return decode_impl(p, peers, workspace, workspace_bytes, stream);
+}
+
+// ---- device memory that other processes of the node can map (CUDA IPC)
+int wsvd_peer_alloc(size_t bytes, void** ptr) {
+  if (!ptr || bytes == 0) return WSVD_ERR_NULL_POINTER;
+  cudaError_t e = cudaMalloc(ptr, bytes);
+  if (e == cudaSuccess) e = cudaMemset(*ptr, 0, bytes);
+  return e == cudaSuccess ? WSVD_OK : cuda_fail(e);
+}
+int wsvd_peer_free(void* ptr) {
+  cudaError_t e = cudaFree(ptr);
+  return e == cudaSuccess ? WSVD_OK : cuda_fail(e);
+}
+int wsvd_peer_export(void* ptr, unsigned char handle[WSVD_PEER_HANDLE_BYTES]) {
+  if (!ptr || !handle) return WSVD_ERR_NULL_POINTER;
+  static_assert(sizeof(cudaIpcMemHandle_t) == WSVD_PEER_HANDLE_BYTES, "handle size");
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, ptr);
+  if (e != cudaSuccess) return cuda_fail(e);
+  memcpy(handle, &h, sizeof(h));
+  return WSVD_OK;
+}
+int wsvd_peer_import(const unsigned char handle[WSVD_PEER_HANDLE_BYTES], void** ptr) {
+  if (!ptr || !handle) return WSVD_ERR_NULL_POINTER;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  cudaError_t e = cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
+  return e == cudaSuccess ? WSVD_OK : cuda_fail(e);
+}
+int wsvd_peer_release(void* ptr) {
+  cudaError_t e = cudaIpcCloseMemHandle(ptr);
   return e == cudaSuccess ? WSVD_OK : cuda_fail(e);
 }
 

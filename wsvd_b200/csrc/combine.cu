@@ -7,16 +7,41 @@
 // length 0 gives zeros; the reference divides by zero there.
 #include "common.cuh"
 
+//
+// With a peer set the kernel is also the head all-gather of a head-sharded group of GPUs: every
+// row is stored into the gathered [B, H_total, D] buffer of EVERY rank (plain stores through
+// peer mappings, NVLink), and the last block of the grid then runs the group's barrier:
+// a system-scope fence, one flag store per peer ("rank r has delivered epoch e"), and a
+// bounded wait until every peer's flag for this rank shows the epoch.  There is no separate
+// collective call and no second pass over the data.
 namespace wsvd {
 namespace {
 
 constexpr int kThreads = 128;
+constexpr unsigned int kPeerWaitTimedOut = 6;
+__device__ unsigned int g_peer_status = 0;
 
+struct PeerArgs {
+  __half* out[WSVD_MAX_PEERS];
+  uint32_t* flags[WSVD_MAX_PEERS];
+  uint32_t* counter;
+  int32_t n_peers, rank, head_offset;
+  uint32_t epoch;
+  uint64_t timeout_ns;
+};
+
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+template <bool kPeers>
 __global__ void __launch_bounds__(kThreads)
 stage2_kernel(const float* __restrict__ mid_o, const float* __restrict__ lse, const int32_t* __restrict__ b_seq_len,
               __half* __restrict__ out, int64_t out_stride_b, int64_t out_stride_h, int n_q_heads, int n_splits,
               int width, int split_len, const __half* __restrict__ wv, int64_t wv_stride_r, int n_kv_heads,
-              int head_dim) {
+              int head_dim, const __grid_constant__ PeerArgs pa) {
   const int h = blockIdx.x, b = blockIdx.y;
   const int n = b_seq_len[b];
   const int ns = n <= 0 ? 0 : min(n_splits, (n + split_len - 1) / split_len);
@@ -35,19 +60,60 @@ stage2_kernel(const float* __restrict__ mid_o, const float* __restrict__ lse, co
     for (int i = 0; i < ns; ++i) o = fmaf(__expf(lse[slot0 + i] - m), mid_o[(slot0 + i) * width + r], o);
     o /= wsum;
   }
-  __half* dst = out + (int64_t)b * out_stride_b + (int64_t)h * out_stride_h;
+  const int64_t doff = (int64_t)b * out_stride_b + (int64_t)(h + (kPeers ? pa.head_offset : 0)) * out_stride_h;
+  auto store = [&](int d, float y) {
+    const __half v = __float2half_rn(y);
+    if constexpr (kPeers) {
+#pragma unroll
+      for (int i = 0; i < WSVD_MAX_PEERS; ++i)
+        if (i < pa.n_peers) pa.out[i][doff + d] = v;
+    } else {
+      out[doff + d] = v;
+    }
+  };
   if (wv == nullptr) {
-    if (r < width) dst[r] = __float2half_rn(o);
-    return;
+    if (r < width) store(r, o);
+  } else {
+    if (r < width) row[r] = o;
+    __syncthreads();
+    const int hk = h / (n_q_heads / n_kv_heads);
+    for (int d = threadIdx.x; d < head_dim; d += kThreads) {
+      float y = 0.f;
+      const __half* w = wv + (int64_t)hk * head_dim + d;
+      for (int k = 0; k < width; ++k) y = fmaf(row[k], __half2float(w[(int64_t)k * wv_stride_r]), y);
+      store(d, y);
+    }
   }
-  if (r < width) row[r] = o;
-  __syncthreads();
-  const int hk = h / (n_q_heads / n_kv_heads);
-  for (int d = threadIdx.x; d < head_dim; d += kThreads) {
-    float y = 0.f;
-    const __half* w = wv + (int64_t)hk * head_dim + d;
-    for (int k = 0; k < width; ++k) y = fmaf(row[k], __half2float(w[(int64_t)k * wv_stride_r]), y);
-    dst[d] = __float2half_rn(y);
+  if constexpr (kPeers) {
+    // ---- group barrier, run by whichever block finishes last
+    __shared__ bool last;
+    __threadfence_system();  // this thread's peer stores are ordered before what follows
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned int done = atomicAdd(pa.counter, 1u) + 1u;
+      last = done == gridDim.x * gridDim.y;
+    }
+    __syncthreads();
+    if (!last) return;
+    if (threadIdx.x == 0) *pa.counter = 0u;  // ready for the next launch
+    __threadfence_system();
+    const int i = threadIdx.x;
+    if (i < pa.n_peers) {
+      // "rank pa.rank has delivered epoch e" into peer i's flag array ...
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pa.flags[i] + pa.rank), "r"(pa.epoch) : "memory");
+      // ... and wait for peer i's word in ours; epochs only grow (wrap-safe comparison)
+      const uint32_t* mine = pa.flags[pa.rank] + i;
+      const uint64_t t0 = global_ns();
+      for (;;) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+        if ((int32_t)(v - pa.epoch) >= 0) break;
+        if (global_ns() - t0 > pa.timeout_ns) {
+          atomicMax(&g_peer_status, kPeerWaitTimedOut);
+          break;
+        }
+      }
+    }
   }
 }
 
@@ -58,11 +124,40 @@ cudaError_t launch_stage2(const float* mid_o, const float* lse, const int32_t* b
                           int width, int split_len, const void* wv, int64_t wv_stride_r, int n_kv_heads,
                           int head_dim, cudaStream_t stream) {
   dim3 grid(n_q_heads, batch);
-  stage2_kernel<<<grid, kThreads, 0, stream>>>(mid_o, lse, b_seq_len, reinterpret_cast<__half*>(out), out_stride_b,
-                                               out_stride_h, n_q_heads, n_splits, width, split_len,
-                                               reinterpret_cast<const __half*>(wv), wv_stride_r, n_kv_heads,
-                                               head_dim);
+  stage2_kernel<false><<<grid, kThreads, 0, stream>>>(mid_o, lse, b_seq_len, reinterpret_cast<__half*>(out),
+                                                      out_stride_b, out_stride_h, n_q_heads, n_splits, width,
+                                                      split_len, reinterpret_cast<const __half*>(wv), wv_stride_r,
+                                                      n_kv_heads, head_dim, PeerArgs{});
   return cudaGetLastError();
+}
+
+cudaError_t launch_stage2_peers(const float* mid_o, const float* lse, const int32_t* b_seq_len,
+                                const WsvdPeerSet& peers, int batch, int n_q_heads, int n_splits, int width,
+                                int split_len, const void* wv, int64_t wv_stride_r, int n_kv_heads, int head_dim,
+                                cudaStream_t stream) {
+  PeerArgs pa{};
+  for (int i = 0; i < peers.n_peers; ++i) {
+    pa.out[i] = reinterpret_cast<__half*>(peers.out[i]);
+    pa.flags[i] = peers.flags[i];
+  }
+  pa.counter = peers.counter;
+  pa.n_peers = peers.n_peers;
+  pa.rank = peers.rank;
+  pa.head_offset = peers.head_offset;
+  pa.epoch = peers.epoch;
+  pa.timeout_ns = peers.timeout_ms > 0 ? (uint64_t)peers.timeout_ms * 1000000ull : 2000000000ull;
+  dim3 grid(n_q_heads, batch);
+  stage2_kernel<true><<<grid, kThreads, 0, stream>>>(mid_o, lse, b_seq_len, nullptr, peers.out_stride_b,
+                                                     peers.out_stride_h, n_q_heads, n_splits, width, split_len,
+                                                     reinterpret_cast<const __half*>(wv), wv_stride_r, n_kv_heads,
+                                                     head_dim, pa);
+  return cudaGetLastError();
+}
+
+cudaError_t read_peer_status(unsigned int* out) { return cudaMemcpyFromSymbol(out, g_peer_status, sizeof(unsigned int)); }
+cudaError_t reset_peer_status() {
+  const unsigned int zero = 0;
+  return cudaMemcpyToSymbol(g_peer_status, &zero, sizeof(unsigned int));
 }
 
 }  // namespace wsvd

@@ -58,6 +58,12 @@ size_t rope_table_bytes(int rows);
 cudaError_t read_tc_status(unsigned int* out);
 cudaError_t reset_tc_status();
 cudaError_t launch_dense_stage1(const DenseArgs& a, cudaStream_t stream);
+cudaError_t launch_stage2_peers(const float* mid_o, const float* lse, const int32_t* b_seq_len,
+                                const WsvdPeerSet& peers, int batch, int n_q_heads, int n_splits, int width,
+                                int split_len, const void* wv, int64_t wv_stride_r, int n_kv_heads, int head_dim,
+                                cudaStream_t stream);
+cudaError_t read_peer_status(unsigned int* out);
+cudaError_t reset_peer_status();
 cudaError_t launch_quant_append(const WsvdQuantAppendParams& p, cudaStream_t stream);
 cudaError_t read_append_status(unsigned int* out);
 cudaError_t reset_append_status();

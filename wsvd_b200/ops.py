@@ -222,6 +222,29 @@ def latent_decode(
 
 
 @torch.no_grad()
+def latent_decode_gather(q, infer_state, latent_k, k_scale, latent_v, v_scale, wk, wk_scale, peers, *, wv=None,
+                         workspace: Optional[torch.Tensor] = None, theta=10000.0, rope_layout="half", split_len=0,
+                         kernel="auto", stream=None) -> None:
+    """This rank's head shard of the op with the head all-gather fused into the merge
+    kernel: rows go straight into every rank's gathered buffer (`peers`, a filled
+    `_lib.PeerSet`, see `wsvd_b200.dist.PeerGather`).  Arguments as `latent_decode`, with the
+    LOCAL heads."""
+    B = int(infer_state.batch_size)
+    q3 = q.view(B, q.shape[-2], q.shape[-1]) if q.dim() != 3 else q
+    rtt = infer_state.req_manager.req_to_token_indexs
+    p, _keep = build_params(q3, infer_state.b_seq_len, infer_state.b_req_idx, rtt, int(infer_state.max_len_in_batch),
+                            latent_k, k_scale, latent_v, v_scale, wk, wk_scale, wv=wv, out=None, theta=theta,
+                            rope_layout=rope_layout, split_len=split_len, kernel=kernel)
+    need = workspace_bytes(p)
+    if workspace is None:
+        workspace = torch.empty(((need + 3) // 4,), dtype=torch.float32, device=q.device)
+    have = workspace.numel() * workspace.element_size()
+    with torch.cuda.device(q.device):
+        check(_lib.lib().wsvd_latent_decode_gather(ctypes.byref(p), ctypes.byref(peers), _ptr(workspace), have,
+                                                   _stream(stream)), "wsvd_latent_decode_gather")
+
+
+@torch.no_grad()
 def latent_decode_stage1(q, latent_k, k_scale, latent_v, v_scale, wk, wk_scale, req_to_token, b_req_idx, b_seq_len,
                          max_len, mid_out, mid_out_lse, block_seq, *, theta=10000.0, rope_layout="half",
                          kernel="auto", stream=None):
