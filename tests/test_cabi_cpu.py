@@ -110,3 +110,77 @@ def test_stage2_argument_checks():
     assert lib.wsvd_decode_stage2(None, f, f, f, 64, 64, 1, 1, 1, 64, 256, None, 0, 1, 0, None) == 1
     assert lib.wsvd_decode_stage2(f, f, f, f, 64, 64, 1, 1, 1, 200, 256, None, 0, 1, 0, None) == 2
     assert lib.wsvd_decode_stage2(f, f, f, f, 64, 64, 0, 1, 1, 64, 256, None, 0, 1, 0, None) == 0
+
+
+def _append_params(**kw):
+    p = _lib.QuantAppendParams()
+    fake = 0x1000
+    for f in ("x_k", "x_v", "latent_k", "latent_v", "k_scale", "v_scale", "req_to_token", "b_req_idx", "b_seq_len"):
+        setattr(p, f, fake)
+    p.batch, p.n_kv_heads, p.rank_k, p.rank_v, p.max_len, p.x_dtype = 2, 4, 64, 48, 100, 1
+    for k, v in kw.items():
+        setattr(p, k, v)
+    return p
+
+
+@pytest.mark.parametrize("field,value,status", [
+    ("x_k", None, 1), ("v_scale", None, 1), ("b_seq_len", None, 1),
+    ("rank_k", 129, 2), ("rank_v", 0, 2), ("n_kv_heads", 0, 2), ("batch", -1, 2),
+    ("x_dtype", 0, 3), ("x_dtype", 9, 3),
+])
+def test_quant_append_validation(field, value, status):
+    p = _append_params(**{field: value})
+    assert _lib.lib().wsvd_latent_quant_append_i8(ctypes.byref(p), None) == status
+
+
+def test_quant_append_empty_batch_is_a_no_op():
+    assert _lib.lib().wsvd_latent_quant_append_i8(ctypes.byref(_append_params(batch=0, x_k=None)), None) == 0
+
+
+def _peer_set(**kw):
+    ps = _lib.PeerSet()
+    for i in range(2):
+        ps.out[i], ps.flags[i] = 0x3000, 0x4000
+    ps.counter = 0x5000
+    ps.n_peers, ps.rank, ps.head_offset, ps.epoch = 2, 0, 0, 1
+    ps.out_stride_b, ps.out_stride_h = 16 * 128, 128
+    for k, v in kw.items():
+        setattr(ps, k, v)
+    return ps
+
+
+@pytest.mark.parametrize("field,value,status", [
+    ("n_peers", 0, 2), ("n_peers", 9, 2), ("rank", 2, 2), ("rank", -1, 2), ("epoch", 0, 2), ("head_offset", -4, 2),
+    ("timeout_ms", -1, 2), ("counter", None, 1),
+])
+def test_gather_peer_set_validation(field, value, status):
+    lib = _lib.lib()
+    ps = _peer_set(**{field: value})
+    assert lib.wsvd_latent_decode_gather(ctypes.byref(_params()), ctypes.byref(ps), ctypes.c_void_p(0x2000), 1 << 30,
+                                         None) == status
+
+
+def test_gather_needs_every_peer_pointer():
+    lib = _lib.lib()
+    ps = _peer_set()
+    ps.flags[1] = None
+    assert lib.wsvd_latent_decode_gather(ctypes.byref(_params()), ctypes.byref(ps), ctypes.c_void_p(0x2000), 1 << 30,
+                                         None) == 1
+    assert lib.wsvd_latent_decode_gather(ctypes.byref(_params()), None, ctypes.c_void_p(0x2000), 1 << 30, None) == 1
+
+
+def test_python_ops_refuse_cpu_tensors():
+    """There is no CPU path: the ops raise before anything is launched."""
+    import torch
+
+    from wsvd_b200 import ops
+    from wsvd_b200.infer_state import InferState
+
+    st = InferState(1, 4, [4], device="cpu")
+    x = torch.zeros(1, 2, 8)
+    with pytest.raises(ValueError, match="CUDA tensor"):
+        ops.latent_quant_append(x, x, st, torch.zeros(4, 2, 8, dtype=torch.int8), torch.zeros(4, 2, dtype=torch.float16),
+                                torch.zeros(4, 2, 8, dtype=torch.int8), torch.zeros(4, 2, dtype=torch.float16))
+    q = torch.zeros(1, 2, 128, dtype=torch.float16)
+    with pytest.raises(ValueError, match="CUDA tensor"):
+        ops.dense_decode(q, st, torch.zeros(4, 2, 128, dtype=torch.float16), torch.zeros(4, 2, 128, dtype=torch.float16))
