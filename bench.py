@@ -41,7 +41,8 @@ DEFAULT_WORKLOAD = "c2_13b_b16_s8192"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one stage-1 launch, from the ncu capture
 # summarised in profiles/latent_decode_stage1_tc_c2.md
-NCU_TRAFFIC_BYTES = {"c2_13b_b16_s8192": 709081088}
+NCU_TRAFFIC_BYTES = {"c2_13b_b16_s8192": 711555328}
+C5_WORKLOAD = "c5_7b_b64_s4096_step"
 
 
 def measured_peaks():
@@ -150,6 +151,134 @@ def run_reference(args, spec):
     print(json.dumps(line), flush=True)
 
 
+def run_c5(args):
+    """The 32-layer decode step (Llama-2-7B architecture, per-head low-rank K/V, batch 64,
+    context 4096): down-projection, int8 quantise-and-append, latent decode attention,
+    o-projection, FFN, for every layer; tensor-parallel by heads at N > 1.  tokens/s."""
+    from wsvd_b200 import ops
+    from wsvd_b200.backbone import BackboneSpec, LatentDecoder
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the op has no CPU path")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch N>1 under torch.distributed.run")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist, pg, collective = None, None, "none"
+    spec = BackboneSpec()
+    B, context = 64, 4096
+    args.warmup = max(args.warmup, 3)
+    steps = min(args.steps, 20)
+    n_e2e = min(steps, 10)
+    capacity = context + args.warmup + steps + n_e2e + 3 + 8
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+        collective = "nccl all_gather of [B,H_local,128] f16 per layer; nccl all_reduce of the FFN output"
+        if args.collective == "fused":
+            from wsvd_b200.dist import PeerGather
+            ok = torch.ones(1, device=dev)
+            try:
+                pg = PeerGather(B, spec.heads, spec.head_dim, device=dev, timeout_ms=10000)
+            except Exception as exc:
+                print(f"[bench] rank {rank}: peer buffers unavailable ({exc}); using NCCL", file=sys.stderr)
+                ok.zero_()
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if ok.item() == 0:
+                pg = None
+            else:
+                collective = ("head all-gather fused into the merge kernel (peer stores + flag barrier) per layer; "
+                              "nccl all_reduce of the FFN output")
+    model = LatentDecoder(spec, B, context, capacity, rank=rank, world=world, device=dev, seed=5, peer_gather=pg)
+    x = (torch.randn(B, spec.hidden, device=dev, dtype=torch.float32) * 0.5).to(torch.float16)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step():
+        model.step(x)
+        model.advance()
+
+    for _ in range(args.warmup):
+        step()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    barrier()
+    ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_step = ms.item()
+
+    x_host = x.cpu().pin_memory()
+    y_host = torch.empty(B, spec.hidden, dtype=torch.float16).pin_memory()
+    x_dev = torch.empty_like(x)
+
+    def e2e_step():
+        x_dev.copy_(x_host, non_blocking=True)
+        y = model.step(x_dev)
+        model.advance()
+        y_host.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(n_e2e):
+        e2e_step()
+    e1.record()
+    barrier()
+    ms2 = torch.tensor([e0.elapsed_time(e1) / n_e2e], device=dev)
+    if world > 1:
+        dist.all_reduce(ms2, op=dist.ReduceOp.MAX)
+    ms_e2e = ms2.item()
+    clocks = sampler.stop() if rank == 0 else None
+    status = torch.tensor([ops.kernel_status()], device=dev)
+    if world > 1:
+        dist.all_reduce(status, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        step_bytes = model.attention_bytes() + model.weight_bytes()
+        achieved = step_bytes / (ms_step * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "decode tokens/s, 32-layer Llama-2-7B-architecture step with per-head low-rank int8 K/V",
+            "value": B / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16 GEMMs (cuBLAS), i8 latents, f32 accumulate/softmax",
+            "data": "synthetic",
+            "config": {"workload": C5_WORKLOAD, "batch": B, "context": context, "layers": spec.layers,
+                       "hidden": spec.hidden, "heads": spec.heads, "heads_per_gpu": spec.heads // world,
+                       "ffn": spec.ffn, "rank_k": spec.rank_k, "rank_v": spec.rank_v,
+                       "parallelism": f"heads x{world}", "collective": collective,
+                       "l2": "caches and weights of one step (GBs per GPU) are larger than the 126 MB L2"},
+            "roofline": {"bound": "hbm", "kernel": "whole step: latent+scale bytes of 32 layers + the rank's weights",
+                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_kind": f"of {peak_kind}", "algorithmic_bytes_per_step": step_bytes,
+                         "attention_bytes_per_step": model.attention_bytes(), "traffic": None},
+            "e2e": {"value": B / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
+            "gpu_launches": steps * spec.layers * 3,
+            "kernel_status": int(status.item()), "clocks": clocks,
+        }), flush=True)
+    if world > 1:
+        if pg is not None:
+            pg.close()
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -167,6 +296,9 @@ def main():
 
     from wsvd_b200 import inputs
 
+    if args.workload == C5_WORKLOAD and args.impl == "ours":
+        run_c5(args)
+        return
     spec = inputs.WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference(args, spec)

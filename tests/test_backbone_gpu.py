@@ -1,0 +1,61 @@
+"""The decode step of the low-rank-KV backbone (down-projection, quantise-and-append, latent
+decode attention, o-projection, FFN) against a CPU restatement built from the oracle."""
+import pytest
+import torch
+
+from oracle.latent_decode_oracle import latent_decode_oracle, quant_append_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _cpu_step(model, x):
+    """fp32 on the CPU with the model's own weights and (cloned) caches."""
+    from wsvd_b200.backbone import _rms_norm, rope_half
+
+    sp, B, Hl = model.spec, model.batch, model.local_heads
+    x = x.float().cpu()
+    lens = model.before.b_seq_len.cpu()
+    idx = model.before.b_req_idx.cpu()
+    table = model.before.req_manager.req_to_token_indexs.cpu()
+    for L in model.layers:
+        W = {k: getattr(L, k).float().cpu() for k in ("Wq", "A_k", "A_v", "Wo", "Wup", "Wgate", "Wdown")}
+        xn = _rms_norm(x)
+        q = rope_half((xn @ W["Wq"]).view(B, Hl, sp.head_dim), lens, sp.theta)
+        xk = (xn @ W["A_k"]).view(B, Hl, sp.rank_k)
+        xv = (xn @ W["A_v"]).view(B, Hl, sp.rank_v)
+        lk, ks, lv, vs = (t.cpu().clone() for t in (L.k_store, L.ks_store, L.v_store, L.vs_store))
+        S = lk.shape[2]
+        T = (B - 1) * Hl * S + S
+        lk_v = lk.as_strided((T, Hl, sp.rank_k), (sp.rank_k, S * sp.rank_k, 1))
+        lv_v = lv.as_strided((T, Hl, sp.rank_v), (sp.rank_v, S * sp.rank_v, 1))
+        ks_v, vs_v = ks.as_strided((T, Hl), (1, S)), vs.as_strided((T, Hl), (1, S))
+        quant_append_oracle(xk, xv, lens, idx, table, lk_v, ks_v, lv_v, vs_v)
+        _, o = latent_decode_oracle(q.to(torch.float16), lens + 1, idx, table, lk_v, ks_v, lv_v, vs_v, L.wk.cpu(),
+                                    wv=L.wv.cpu(), theta=sp.theta)
+        x = x + o.reshape(B, -1).float() @ W["Wo"]
+        h = _rms_norm(x)
+        x = x + ((h @ W["Wup"]) * torch.nn.functional.silu(h @ W["Wgate"])) @ W["Wdown"]
+    return x
+
+
+def test_two_layer_step_matches_cpu_restatement():
+    from wsvd_b200 import ops
+    from wsvd_b200.backbone import BackboneSpec, LatentDecoder
+
+    spec = BackboneSpec(layers=2, hidden=512, heads=4, head_dim=128, ffn=1024, rank_k=64, rank_v=64)
+    model = LatentDecoder(spec, batch=3, context=300, capacity=310, device="cuda", seed=1)
+    x = (torch.randn(3, 512, generator=torch.Generator().manual_seed(2)) * 0.5).to(torch.float16).cuda()
+    want = _cpu_step(model, x)  # before the GPU step touches the caches
+    got = model.step(x)
+    torch.cuda.synchronize()
+    assert ops.kernel_status() == 0
+    err = (got.float().cpu() - want).abs().max().item()
+    scale = want.abs().max().item()
+    # f16 GEMMs against fp32 ones, and a latent that rounds the other way now and then
+    assert err <= 3e-2 * scale, (err, scale)
+    # the token landed where the next step will look for it
+    model.advance()
+    got2 = model.step(got)
+    torch.cuda.synchronize()
+    assert torch.isfinite(got2).all() and ops.kernel_status() == 0
+    assert int(model.after.b_seq_len[0]) == 302
