@@ -438,7 +438,8 @@ def main():
     q_host = case.q.cpu().pin_memory()
     len_host = st.b_seq_len.cpu().pin_memory()
     req_host = st.b_req_idx.cpu().pin_memory()
-    out_host = torch.empty(B, H, D, dtype=torch.float16).pin_memory()
+    # (with the fused gather the step's result is the gathered [B, H_total, D] buffer)
+    out_host = torch.empty(B, H * (world if pg is not None else 1), D, dtype=torch.float16).pin_memory()
     q_dev, len_dev, req_dev = torch.empty_like(case.q), torch.empty_like(st.b_seq_len), torch.empty_like(st.b_req_idx)
     from wsvd_b200.infer_state import InferState
     st2 = InferState(B, st.max_len_in_batch, lens, device=dev, req_to_token=st.req_manager.req_to_token_indexs)
@@ -451,7 +452,6 @@ def main():
         if pg is not None:
             o = pg.decode(q_dev, st2, case.latent_k, case.k_scale, case.latent_v, case.v_scale, case.wk, None,
                           wv=case.wv, workspace=ws, split_len=args.split_len, kernel=args.kernel)
-            o = o[:, rank * H:(rank + 1) * H]  # the caller of this rank reads its heads back
         else:
             o = op(q_dev, st2, H, D, case.latent_k, case.k_scale, case.latent_v, case.v_scale, case.wk, None,
                    wv=case.wv, out=out, workspace=ws, split_len=args.split_len, kernel=args.kernel)

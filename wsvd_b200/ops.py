@@ -232,10 +232,20 @@ def latent_decode_gather(q, infer_state, latent_k, k_scale, latent_v, v_scale, w
     B = int(infer_state.batch_size)
     q3 = q.view(B, q.shape[-2], q.shape[-1]) if q.dim() != 3 else q
     rtt = infer_state.req_manager.req_to_token_indexs
-    p, _keep = build_params(q3, infer_state.b_seq_len, infer_state.b_req_idx, rtt, int(infer_state.max_len_in_batch),
-                            latent_k, k_scale, latent_v, v_scale, wk, wk_scale, wv=wv, out=None, theta=theta,
-                            rope_layout=rope_layout, split_len=split_len, kernel=kernel)
-    need = workspace_bytes(p)
+    max_len = int(infer_state.max_len_in_batch)
+    # same per-call-signature cache of the validated argument block as latent_decode
+    key = ("gather", _sig(q3), _sig(infer_state.b_seq_len), _sig(infer_state.b_req_idx), _sig(rtt), max_len,
+           _sig(latent_k), _sig(k_scale), _sig(latent_v), _sig(v_scale), _sig(wk), _sig(wk_scale), _sig(wv),
+           float(theta), rope_layout, int(split_len), kernel)
+    hit = _CALLS.get(key)
+    if hit is None:
+        p, _keep = build_params(q3, infer_state.b_seq_len, infer_state.b_req_idx, rtt, max_len, latent_k, k_scale,
+                                latent_v, v_scale, wk, wk_scale, wv=wv, out=None, theta=theta,
+                                rope_layout=rope_layout, split_len=split_len, kernel=kernel)
+        if len(_CALLS) >= 64:
+            _CALLS.clear()
+        hit = _CALLS[key] = (p, workspace_bytes(p))
+    p, need = hit
     if workspace is None:
         workspace = torch.empty(((need + 3) // 4,), dtype=torch.float32, device=q.device)
     have = workspace.numel() * workspace.element_size()
