@@ -173,7 +173,7 @@ def run_c5(args):
     args.warmup = max(args.warmup, 3)
     steps = min(args.steps, 20)
     n_e2e = min(steps, 10)
-    capacity = context + args.warmup + steps + n_e2e + 3 + 8
+    capacity = context + args.warmup + steps + n_e2e + 3 + 8 + 2
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
@@ -200,7 +200,15 @@ def run_c5(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    graph = None
+    if world == 1 and not args.no_graph:
+        graph, y_graph = model.capture(x)  # one CUDA graph replayed per step (advances the context by one)
+
     def step():
+        if graph is not None:
+            graph.replay()
+            model.context += 1  # the graph advanced the device-side lengths
+            return
         model.step(x)
         model.advance()
 
@@ -226,10 +234,16 @@ def run_c5(args):
     x_dev = torch.empty_like(x)
 
     def e2e_step():
-        x_dev.copy_(x_host, non_blocking=True)
-        y = model.step(x_dev)
-        model.advance()
-        y_host.copy_(y, non_blocking=True)
+        if graph is not None:
+            x.copy_(x_host, non_blocking=True)  # the graph reads its input from x
+            graph.replay()
+            model.context += 1
+            y_host.copy_(y_graph, non_blocking=True)
+        else:
+            x_dev.copy_(x_host, non_blocking=True)
+            y = model.step(x_dev)
+            model.advance()
+            y_host.copy_(y, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     for _ in range(3):
@@ -262,6 +276,7 @@ def run_c5(args):
                        "hidden": spec.hidden, "heads": spec.heads, "heads_per_gpu": spec.heads // world,
                        "ffn": spec.ffn, "rank_k": spec.rank_k, "rank_v": spec.rank_v,
                        "parallelism": f"heads x{world}", "collective": collective,
+                       "launch": "one CUDA graph per step" if graph is not None else "eager, from Python",
                        "l2": "caches and weights of one step (GBs per GPU) are larger than the 126 MB L2"},
             "roofline": {"bound": "hbm", "kernel": "whole step: latent+scale bytes of 32 layers + the rank's weights",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -289,6 +304,7 @@ def main():
     ap.add_argument("--kernel", default="auto", choices=["auto", "generic", "tc"])
     ap.add_argument("--split-len", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="c5 step at N=1: launch from Python instead of one CUDA graph")
     ap.add_argument("--collective", default="fused", choices=["fused", "nccl"],
                     help="N>1: head all-gather fused into the merge kernel (peer stores), or an NCCL all_gather")
     ap.add_argument("--no-dense", action="store_true", help="skip the dense f16 baseline kernel timing")

@@ -59,3 +59,23 @@ def test_two_layer_step_matches_cpu_restatement():
     torch.cuda.synchronize()
     assert torch.isfinite(got2).all() and ops.kernel_status() == 0
     assert int(model.after.b_seq_len[0]) == 302
+
+
+def test_captured_step_replays_like_the_eager_one():
+    from wsvd_b200 import ops
+    from wsvd_b200.backbone import BackboneSpec, LatentDecoder
+
+    spec = BackboneSpec(layers=2, hidden=512, heads=4, head_dim=128, ffn=1024, rank_k=64, rank_v=64)
+    x = (torch.randn(3, 512, generator=torch.Generator().manual_seed(4)) * 0.5).to(torch.float16).cuda()
+    eager = LatentDecoder(spec, batch=3, context=200, capacity=210, device="cuda", seed=9)
+    eager.step(x)
+    eager.advance()
+    want = eager.step(x)                      # the second step
+    graphed = LatentDecoder(spec, batch=3, context=200, capacity=210, device="cuda", seed=9)
+    graph, y = graphed.capture(x)             # runs the first step while warming up
+    graph.replay()                            # the second step
+    graphed.context += 1
+    torch.cuda.synchronize()
+    assert ops.kernel_status() == 0
+    assert torch.equal(y, want)
+    assert int(graphed.after.b_seq_len[0]) == int(eager.after.b_seq_len[0]) + 1  # eager has not advanced yet

@@ -179,6 +179,33 @@ class LatentDecoder:
             x = x + f
         return x
 
+    def capture(self, x: torch.Tensor):
+        """Capture `step(x)` followed by the length update in a CUDA graph (single GPU, NCCL
+        gather excluded: the fused gather's epoch is a host-side argument).  The split plan is
+        made for the cache capacity, so one graph serves every later step.  Returns
+        (graph, output tensor); replay with graph.replay() after writing the new input into x."""
+        assert self.pg is None and self.world == 1
+        self.before.max_len_in_batch = self.capacity
+        self.after.max_len_in_batch = self.capacity
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):  # warm-up: workspace, position table, cuBLAS handles
+            self.step(x)
+            self._advance_device()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            y = self.step(x)
+            self._advance_device(host=False)  # recorded, not run: the caller counts replays in self.context
+        return graph, y
+
+    def _advance_device(self, host: bool = True):
+        if host:
+            self.context += 1
+        self.before.b_seq_len += 1
+        self.after.b_seq_len += 1
+
     def advance(self):
         """Make the appended token part of the context (needs capacity for the next one)."""
         self.context += 1

@@ -78,10 +78,20 @@ stage2_kernel(const float* __restrict__ mid_o, const float* __restrict__ lse, co
     __syncthreads();
     const int hk = h / (n_q_heads / n_kv_heads);
     for (int d = threadIdx.x; d < head_dim; d += kThreads) {
-      float y = 0.f;
+      // four partial sums and a deep unroll: the loads of U_v (L2) are independent of one
+      // another, so many are in flight at once instead of one per dependent step
+      float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
       const __half* w = wv + (int64_t)hk * head_dim + d;
-      for (int k = 0; k < width; ++k) y = fmaf(row[k], __half2float(w[(int64_t)k * wv_stride_r]), y);
-      store(d, y);
+      int k = 0;
+#pragma unroll 4
+      for (; k + 4 <= width; k += 4) {
+        y0 = fmaf(row[k], __half2float(__ldg(w + (int64_t)k * wv_stride_r)), y0);
+        y1 = fmaf(row[k + 1], __half2float(__ldg(w + (int64_t)(k + 1) * wv_stride_r)), y1);
+        y2 = fmaf(row[k + 2], __half2float(__ldg(w + (int64_t)(k + 2) * wv_stride_r)), y2);
+        y3 = fmaf(row[k + 3], __half2float(__ldg(w + (int64_t)(k + 3) * wv_stride_r)), y3);
+      }
+      for (; k < width; ++k) y0 = fmaf(row[k], __half2float(__ldg(w + (int64_t)k * wv_stride_r)), y0);
+      store(d, (y0 + y1) + (y2 + y3));
     }
   }
   if constexpr (kPeers) {
