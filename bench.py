@@ -182,7 +182,8 @@ def run_c5(args):
             from wsvd_b200.dist import PeerGather
             ok = torch.ones(1, device=dev)
             try:
-                pg = PeerGather(B, spec.heads, spec.head_dim, device=dev, timeout_ms=10000)
+                pg = PeerGather(B, spec.heads, spec.head_dim, device=dev, timeout_ms=10000,
+                                device_epoch=not args.no_graph)
             except Exception as exc:
                 print(f"[bench] rank {rank}: peer buffers unavailable ({exc}); using NCCL", file=sys.stderr)
                 ok.zero_()
@@ -201,7 +202,7 @@ def run_c5(args):
         torch.cuda.synchronize()
 
     graph = None
-    if world == 1 and not args.no_graph:
+    if not args.no_graph:
         graph, y_graph = model.capture(x)  # one CUDA graph replayed per step (advances the context by one)
 
     def step():
@@ -295,6 +296,9 @@ def run_c5(args):
 
 
 def main():
+    # NCCL writes its version banner to stdout at NCCL_DEBUG=VERSION; stdout is for the one JSON line
+    if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+        os.environ["NCCL_DEBUG"] = "WARN"
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
@@ -304,7 +308,7 @@ def main():
     ap.add_argument("--kernel", default="auto", choices=["auto", "generic", "tc"])
     ap.add_argument("--split-len", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-graph", action="store_true", help="c5 step at N=1: launch from Python instead of one CUDA graph")
+    ap.add_argument("--no-graph", action="store_true", help="c5 step: launch from Python instead of one CUDA graph")
     ap.add_argument("--collective", default="fused", choices=["fused", "nccl"],
                     help="N>1: head all-gather fused into the merge kernel (peer stores), or an NCCL all_gather")
     ap.add_argument("--no-dense", action="store_true", help="skip the dense f16 baseline kernel timing")

@@ -222,7 +222,10 @@ int wsvd_latent_quant_append_i8(const WsvdQuantAppendParams* p, void* stream);
  *  - out[i], flags[i]: rank i's gathered buffer and flag array (WSVD_MAX_PEERS uint32,
  *    zero before the first call) as mapped in THIS process; entry `rank` is local memory.
  *    counter: one local uint32, zero before the first call.
- *  - epoch: the same value on all ranks for a given step, never 0, +1 per step.
+ *  - epoch: the same value on all ranks for a given step, never 0, +1 per step.  When
+ *    epoch_counter is set the kernel takes *epoch_counter + 1 instead and stores it back, so
+ *    that nothing in the argument block changes from step to step and the call can sit in a
+ *    captured CUDA graph; `epoch` is then ignored.
  *  - Every rank must make the call with the same batch; p->out is ignored; p->n_q_heads is
  *    the LOCAL head count and head_offset the first global head of the shard.
  *  - Reuse: a rank may overwrite a peer's buffer for step e+1 while that peer still reads
@@ -242,6 +245,7 @@ typedef struct WsvdPeerSet {
   uint32_t epoch;
   int64_t out_stride_b, out_stride_h;  /* of the gathered buffers, in f16 elements */
   int32_t timeout_ms;
+  uint32_t* epoch_counter;  /* optional: local uint32, zero before the first call, equal on all ranks */
 } WsvdPeerSet;
 int wsvd_latent_decode_gather(const WsvdLatentDecodeParams* p, const WsvdPeerSet* peers, void* workspace,
                               size_t workspace_bytes, void* stream);

@@ -137,3 +137,26 @@ def test_two_gpus_peer_stores():
     ret = mgr.dict()
     mp.spawn(_two_gpu_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
     assert dict(ret) == {0: "ok", 1: "ok"}
+
+
+def test_device_side_epoch_counts_the_steps():
+    """epoch_counter mode: the kernel takes the step number from device memory, so the same
+    argument block serves step after step (what a captured CUDA graph replays)."""
+    from wsvd_b200 import _lib, ops
+
+    H, B = 4, 2
+    case = inputs.make_case(B, H, 128, 64, 64, [300, 200], 320, seed=3).to("cuda")
+    out = torch.zeros(B, H, 64, dtype=torch.float16, device="cuda")
+    flags = torch.zeros(_lib.MAX_PEERS, dtype=torch.int32, device="cuda")
+    counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+    epoch_dev = torch.zeros(1, dtype=torch.int32, device="cuda")
+    q, lk, ks, lv, vs, wk, wv = _shard_case(case, slice(0, H))
+    ps = _peer_set(_lib, [out], [flags], counter, 0, 0, 0, H, 64)   # epoch 0: taken from the device
+    ps.epoch_counter = epoch_dev.data_ptr()
+    for step in range(1, 4):
+        out.zero_()
+        ops.latent_decode_gather(q, case.infer_state, lk, ks, lv, vs, wk, None, ps)
+        torch.cuda.synchronize()
+        assert ops.kernel_status() == 0
+        assert int(epoch_dev.item()) == step and int(flags[0].item()) == step
+        assert_close(out, oracle_for(case.to("cpu")), f"step {step}")

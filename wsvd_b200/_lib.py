@@ -134,7 +134,7 @@ class PeerSet(ctypes.Structure):
         ("out", ctypes.c_void_p * MAX_PEERS), ("flags", ctypes.c_void_p * MAX_PEERS), ("counter", ctypes.c_void_p),
         ("n_peers", ctypes.c_int32), ("rank", ctypes.c_int32), ("head_offset", ctypes.c_int32),
         ("epoch", ctypes.c_uint32), ("out_stride_b", ctypes.c_int64), ("out_stride_h", ctypes.c_int64),
-        ("timeout_ms", ctypes.c_int32),
+        ("timeout_ms", ctypes.c_int32), ("epoch_counter", ctypes.c_void_p),
     ]
 
 

@@ -180,11 +180,12 @@ class LatentDecoder:
         return x
 
     def capture(self, x: torch.Tensor):
-        """Capture `step(x)` followed by the length update in a CUDA graph (single GPU, NCCL
-        gather excluded: the fused gather's epoch is a host-side argument).  The split plan is
-        made for the cache capacity, so one graph serves every later step.  Returns
-        (graph, output tensor); replay with graph.replay() after writing the new input into x."""
-        assert self.pg is None and self.world == 1
+        """Capture `step(x)` followed by the length update in a CUDA graph.  The split plan is
+        made for the cache capacity, so one graph serves every later step.  With several ranks
+        the fused gather must keep its epoch on the device (`PeerGather(device_epoch=True)`);
+        the NCCL collectives are captured as they are.  Returns (graph, output tensor); replay
+        with graph.replay() after writing the new input into x."""
+        assert self.pg is None or self.pg.device_epoch
         self.before.max_len_in_batch = self.capacity
         self.after.max_len_in_batch = self.capacity
         side = torch.cuda.Stream(device=self.device)

@@ -267,7 +267,8 @@ int wsvd_latent_decode_gather(const WsvdLatentDecodeParams* p, const WsvdPeerSet
   if (!peers) return WSVD_ERR_NULL_POINTER;
   if (peers->n_peers < 1 || peers->n_peers > WSVD_MAX_PEERS || peers->rank < 0 || peers->rank >= peers->n_peers)
     return WSVD_ERR_BAD_SHAPE;
-  if (peers->epoch == 0 || peers->head_offset < 0 || peers->timeout_ms < 0) return WSVD_ERR_BAD_SHAPE;
+  if ((peers->epoch == 0 && !peers->epoch_counter) || peers->head_offset < 0 || peers->timeout_ms < 0)
+    return WSVD_ERR_BAD_SHAPE;
   if (!peers->counter) return WSVD_ERR_NULL_POINTER;
   for (int i = 0; i < peers->n_peers; ++i)
     if (!peers->out[i] || !peers->flags[i]) return WSVD_ERR_NULL_POINTER;

@@ -25,6 +25,7 @@ struct PeerArgs {
   __half* out[WSVD_MAX_PEERS];
   uint32_t* flags[WSVD_MAX_PEERS];
   uint32_t* counter;
+  uint32_t* epoch_counter;
   int32_t n_peers, rank, head_offset;
   uint32_t epoch;
   uint64_t timeout_ns;
@@ -106,18 +107,25 @@ stage2_kernel(const float* __restrict__ mid_o, const float* __restrict__ lse, co
     __syncthreads();
     if (!last) return;
     if (threadIdx.x == 0) *pa.counter = 0u;  // ready for the next launch
+    // the step's epoch: the caller's, or one more than the device-side count of past steps
+    uint32_t epoch = pa.epoch;
+    if (pa.epoch_counter != nullptr) {
+      epoch = *reinterpret_cast<volatile uint32_t*>(pa.epoch_counter) + 1u;
+      __syncthreads();  // every thread of this (last) block has read the old count
+      if (threadIdx.x == 0) *pa.epoch_counter = epoch;
+    }
     __threadfence_system();
     const int i = threadIdx.x;
     if (i < pa.n_peers) {
       // "rank pa.rank has delivered epoch e" into peer i's flag array ...
-      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pa.flags[i] + pa.rank), "r"(pa.epoch) : "memory");
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pa.flags[i] + pa.rank), "r"(epoch) : "memory");
       // ... and wait for peer i's word in ours; epochs only grow (wrap-safe comparison)
       const uint32_t* mine = pa.flags[pa.rank] + i;
       const uint64_t t0 = global_ns();
       for (;;) {
         uint32_t v;
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
-        if ((int32_t)(v - pa.epoch) >= 0) break;
+        if ((int32_t)(v - epoch) >= 0) break;
         if (global_ns() - t0 > pa.timeout_ns) {
           atomicMax(&g_peer_status, kPeerWaitTimedOut);
           break;
@@ -151,6 +159,7 @@ cudaError_t launch_stage2_peers(const float* mid_o, const float* lse, const int3
     pa.flags[i] = peers.flags[i];
   }
   pa.counter = peers.counter;
+  pa.epoch_counter = peers.epoch_counter;
   pa.n_peers = peers.n_peers;
   pa.rank = peers.rank;
   pa.head_offset = peers.head_offset;

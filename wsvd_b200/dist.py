@@ -63,9 +63,16 @@ class PeerGather:
     all ranks' buffers over NVLink and runs the group barrier in its last block, so when
     the returned tensor is read on the same stream it holds every rank's heads.  No NCCL
     call is made per step; torch.distributed is used once, to exchange the handles.
+
+    `device_epoch=True` keeps the step count on the device and always uses the first buffer, so
+    the argument block never changes and `decode` can be captured in a CUDA graph.  With one
+    buffer the caller has to keep a group synchronisation between consecutive steps (in the
+    decoder backbone the all-reduce of the FFN output is one): otherwise a fast rank could
+    overwrite rows that a slow rank has not read yet.
     """
 
-    def __init__(self, batch: int, heads_total: int, head_dim: int, group=None, device=None, timeout_ms: int = 0):
+    def __init__(self, batch: int, heads_total: int, head_dim: int, group=None, device=None, timeout_ms: int = 0,
+                 device_epoch: bool = False):
         import ctypes
 
         from . import _lib
@@ -79,6 +86,7 @@ class PeerGather:
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.shape = (int(batch), int(heads_total), int(head_dim))
         self.timeout_ms = int(timeout_ms)
+        self.device_epoch = bool(device_epoch)
         out_bytes = batch * heads_total * head_dim * 2
         self._out_bytes = (out_bytes + 255) // 256 * 256
         total = 2 * self._out_bytes + 256  # two buffers | flags (MAX_PEERS u32) | counter
@@ -109,8 +117,11 @@ class PeerGather:
 
     def peer_set(self):
         """The argument block of the next step (advances the epoch)."""
-        self.epoch += 1
-        parity = self.epoch & 1
+        if self.device_epoch:
+            parity = 0
+        else:
+            self.epoch += 1
+            parity = self.epoch & 1
         ps = self._lib.PeerSet()
         for r, b in enumerate(self._bases):
             ps.out[r] = b + parity * self._out_bytes
@@ -118,6 +129,8 @@ class PeerGather:
         ps.counter = self._base + 2 * self._out_bytes + 128
         ps.n_peers, ps.rank, ps.head_offset = self.world, self.rank, self.shard.start
         ps.epoch = self.epoch
+        if self.device_epoch:
+            ps.epoch_counter = self._base + 2 * self._out_bytes + 192
         B, H, D = self.shape
         ps.out_stride_b, ps.out_stride_h = H * D, D
         ps.timeout_ms = self.timeout_ms
