@@ -202,7 +202,9 @@ def run_c5(args):
         torch.cuda.synchronize()
 
     graph = None
-    if not args.no_graph:
+    # (with the NCCL head gather the step is launched from Python: a run that captured it in a graph
+    # did not finish and was not repeated)
+    if not args.no_graph and (world == 1 or pg is not None):
         graph, y_graph = model.capture(x)  # one CUDA graph replayed per step (advances the context by one)
 
     def step():

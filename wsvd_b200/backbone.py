@@ -182,10 +182,10 @@ class LatentDecoder:
     def capture(self, x: torch.Tensor):
         """Capture `step(x)` followed by the length update in a CUDA graph.  The split plan is
         made for the cache capacity, so one graph serves every later step.  With several ranks
-        the fused gather must keep its epoch on the device (`PeerGather(device_epoch=True)`);
-        the NCCL collectives are captured as they are.  Returns (graph, output tensor); replay
+        the head gather has to be the fused one with its epoch on the device
+        (`PeerGather(device_epoch=True)`); the FFN's NCCL all-reduce is captured as it is.  Returns (graph, output tensor); replay
         with graph.replay() after writing the new input into x."""
-        assert self.pg is None or self.pg.device_epoch
+        assert (self.world == 1 and self.pg is None) or (self.pg is not None and self.pg.device_epoch)
         self.before.max_len_in_batch = self.capacity
         self.after.max_len_in_batch = self.capacity
         side = torch.cuda.Stream(device=self.device)
