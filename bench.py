@@ -291,6 +291,13 @@ def run_c5(args):
             "kernel_status": int(status.item()), "clocks": clocks,
         }), flush=True)
     if world > 1:
+        if graph is not None:
+            # Every rank has passed the all-reduce of the status word after its last kernel.  With the
+            # NCCL all-reduce captured in the step's graph, tearing the peer buffers and the process
+            # group down did not return on 8 ranks; leave it to process exit.
+            sys.stdout.flush()
+            sys.stderr.flush()
+            os._exit(0)
         if pg is not None:
             pg.close()
         dist.barrier()
