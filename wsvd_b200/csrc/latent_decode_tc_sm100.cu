@@ -554,6 +554,47 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       const float* qg = qs + g * 128;
       const int tid = threadIdx.x & 127;
       const int64_t col = (int64_t)hk * 128;
+      if (wk_vec && !interleaved) {
+        // Common case (f16 wk, half-split pairing): packed f16 arithmetic.  The operands are
+        // rounded to f16 for the MMA anyway; forming them with one extra f16 rounding of a
+        // product keeps the error of the scores within a few 1e-5.  This thread's chunk of 8
+        // frequencies is the same for its four ranks, so q is converted once.
+        const int ic = tid & 7;
+        __half2 qa[4], qb[4], nqa[4];
+        {
+          const float4 a0 = *reinterpret_cast<const float4*>(qg + ic * 8);
+          const float4 a1 = *reinterpret_cast<const float4*>(qg + ic * 8 + 4);
+          const float4 b0 = *reinterpret_cast<const float4*>(qg + 64 + ic * 8);
+          const float4 b1 = *reinterpret_cast<const float4*>(qg + 64 + ic * 8 + 4);
+          qa[0] = __floats2half2_rn(a0.x, a0.y);
+          qa[1] = __floats2half2_rn(a0.z, a0.w);
+          qa[2] = __floats2half2_rn(a1.x, a1.y);
+          qa[3] = __floats2half2_rn(a1.z, a1.w);
+          qb[0] = __floats2half2_rn(b0.x, b0.y);
+          qb[1] = __floats2half2_rn(b0.z, b0.w);
+          qb[2] = __floats2half2_rn(b1.x, b1.y);
+          qb[3] = __floats2half2_rn(b1.z, b1.w);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) nqa[e] = __hneg2(qa[e]);
+        }
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          const int r = (tid + 128 * it) >> 3;
+          const __half2* ua = reinterpret_cast<const __half2*>(&wpre[2 * it]);      // U[d = ic*8 .. +7]
+          const __half2* ub = reinterpret_cast<const __half2*>(&wpre[2 * it + 1]);  // U[64 + ic*8 .. +7]
+          __align__(16) __half2 pv[4];
+          __align__(16) __half2 qv[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            pv[e] = __hfma2(qa[e], ua[e], __hmul2(qb[e], ub[e]));   // P = q_i U_i + q_{i+64} U_{i+64}
+            qv[e] = __hfma2(nqa[e], ub[e], __hmul2(qb[e], ua[e]));  // Q = q_{i+64} U_i - q_i U_{i+64}
+          }
+          const int nrow = g * 64 + r;
+          const uint32_t off = nrow * 128 + ((ic ^ (nrow & 7)) << 4);
+          *reinterpret_cast<uint4*>(sm + kOffB + off) = *reinterpret_cast<const uint4*>(pv);
+          *reinterpret_cast<uint4*>(sm + kOffB + kBHalfBytes + off) = *reinterpret_cast<const uint4*>(qv);
+        }
+      } else
 #pragma unroll
       for (int it = 0; it < 4; ++it) {
         const int task = tid + 128 * it;
