@@ -331,21 +331,22 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
 
   // ---- set-up: barriers + tensor memory (MMA warp), scaled q to shared memory (epilogue warps)
   if (warp == kMmaWarp) {
-    if (lane == 0) {
-      for (int s = 0; s < kStages; ++s) {
-        mbar_init(bar_full(s), 32);   // one arrive per lane of the warp that issues the copy
-        mbar_init(bar_empty(s), 2);   // the two epilogue warps that own the half-tile's tokens
-      }
-      for (int i = 0; i < 2; ++i) {
-        mbar_init(bar_a_full(i), 1);
-        mbar_init(bar_a_empty(i), 1);
-        mbar_init(bar_w_full(i), 1);
-        mbar_init(bar_w_empty(i), 4 * G);
-      }
+    // one lane per barrier: lanes 0..11 the ring's full/empty pairs, lanes 12..15 the pairs of
+    // the table and W buffers, lane 16 the [P;Q] barrier
+    if (lane < kStages) {
+      mbar_init(bar_full(lane), 32);   // one arrive per lane of the warp that issues the copy
+      mbar_init(bar_empty(lane), 2);   // the two epilogue warps that own the half-tile's tokens
+      reinterpret_cast<volatile int*>(sm + kOffIssued)[lane] = 0;
+    } else if (lane < kStages + 2) {
+      mbar_init(bar_a_full(lane - kStages), 1);
+      mbar_init(bar_a_empty(lane - kStages), 1);
+    } else if (lane < kStages + 4) {
+      mbar_init(bar_w_full(lane - kStages - 2), 1);
+      mbar_init(bar_w_empty(lane - kStages - 2), 4 * G);
+    } else if (lane == kStages + 4) {
       mbar_init(bar_pq, 4 * G);
-      for (int i = 0; i < kStages; ++i) reinterpret_cast<volatile int*>(sm + kOffIssued)[i] = 0;
-      fence_barrier_init();
     }
+    fence_barrier_init();
     __syncwarp();
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
     tmem_relinquish();
