@@ -447,6 +447,20 @@ def main():
     ms_total = timed(step, args.steps)
     ms_step = ms_total / args.steps
 
+    # ---- the same step replayed from a CUDA graph (one GPU): what a serving loop that captures its
+    #      decode step pays; matters for the small workloads, which are bound by launch latency ----
+    ms_graph = None
+    if world == 1:
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            stream = torch.cuda.current_stream()  # step() launches on `stream`
+            step()
+        stream = torch.cuda.current_stream()
+        for _ in range(3):
+            g.replay()
+        ms_graph = timed(g.replay, args.steps) / args.steps
+
     # ---- dominant kernel alone (stage 1), for the roofline ----
     mid_o = ws[: B * H * n_splits * spec.rank_v]
     lse = ws[B * H * n_splits * spec.rank_v:]
@@ -505,6 +519,7 @@ def main():
         line = {
             "metric": METRIC, "value": bytes_total / (ms_step * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "us_per_layer": ms_step * 1e3,
+            "us_per_layer_cuda_graph": None if ms_graph is None else ms_graph * 1e3,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "i8 latents, f16 tensor-core operands, f32 accumulate/softmax", "data": "synthetic",
             "config": {
