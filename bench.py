@@ -12,6 +12,7 @@ batch of one decoder layer.  Rank 0 prints ONE JSON line.
   that same shape (weak scaling: 40 local heads per GPU) and the step ends with the
   path's one exchange, the all-gather of the [B, H_local, 128] outputs, fused into the
   merge kernel as peer stores (--collective nccl: the library all-gather instead).
+  --shard-heads divides the named workload's own heads over the ranks instead (strong scaling).
 * `value` = algorithmic latent+scale bytes of all ranks / max-over-ranks device time.
 * `e2e` = the same step through the public Python op with the per-step inputs (q and
   the batch metadata) copied from pinned host memory and the result copied back to the
@@ -317,6 +318,9 @@ def main():
     ap.add_argument("--kernel", default="auto", choices=["auto", "generic", "tc"])
     ap.add_argument("--split-len", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--shard-heads", action="store_true",
+                    help="N>1: divide the workload's heads over the ranks (strong scaling) instead of giving "
+                         "every rank a full-size shard (weak scaling, the default)")
     ap.add_argument("--no-graph", action="store_true", help="c5 step: launch from Python instead of one CUDA graph")
     ap.add_argument("--collective", default="fused", choices=["fused", "nccl"],
                     help="N>1: head all-gather fused into the merge kernel (peer stores), or an NCCL all_gather")
@@ -354,8 +358,15 @@ def main():
     args.warmup = max(args.warmup, 3)
 
     # ---- workload: this rank's head shard, generated on the device ----
-    shard_spec = inputs.WorkloadSpec(**{**spec.__dict__, "seed": spec.seed + 7919 * rank})
-    case = inputs.make_workload(shard_spec, device=dev)
+    if args.shard_heads and world > 1:
+        # strong scaling: the named workload's heads are divided over the ranks
+        if spec.heads % world:
+            raise SystemExit(f"{spec.heads} heads do not divide over {world} ranks")
+        per = spec.heads // world
+        case = inputs.make_workload(spec, device=dev, heads=slice(rank * per, (rank + 1) * per))
+    else:
+        shard_spec = inputs.WorkloadSpec(**{**spec.__dict__, "seed": spec.seed + 7919 * rank})
+        case = inputs.make_workload(shard_spec, device=dev)
     st = case.infer_state
     B, H, D = case.q.shape
     lens = case.seq_lens
@@ -520,7 +531,8 @@ def main():
             "metric": METRIC, "value": bytes_total / (ms_step * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "us_per_layer": ms_step * 1e3,
             "us_per_layer_cuda_graph": None if ms_graph is None else ms_graph * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "higher_is_better": True, "scaling": "strong" if args.shard_heads and world > 1 else "weak",
+            "vs_baseline": None,
             "dtype": "i8 latents, f16 tensor-core operands, f32 accumulate/softmax", "data": "synthetic",
             "config": {
                 "workload": spec.name, "batch": spec.batch, "heads_per_gpu": H, "head_dim": D,
