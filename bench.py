@@ -8,12 +8,15 @@ batch of one decoder layer.  Rank 0 prints ONE JSON line.
 
 * N = 1: workload c2 (LLaVA-1.5-13B shape: B16, 40 heads, head_dim 128, rank 64/64,
   context 8192), inputs resident in HBM and larger than L2.
-* N > 1 (launched under torchrun, one rank per GPU): every rank owns a head shard of
-  that same shape (weak scaling: 40 local heads per GPU) and the step ends with the
+* N > 1 (launched under torchrun, one rank per GPU): the workload's own heads are divided
+  over the ranks (strong scaling: 40 -> 20/10/5 heads per GPU) and the step ends with the
   path's one exchange, the all-gather of the [B, H_local, 128] outputs, fused into the
   merge kernel as peer stores (--collective nccl: the library all-gather instead).
-  --shard-heads divides the named workload's own heads over the ranks instead (strong scaling).
+  --weak gives every rank a full-size shard of its own instead (weak scaling).
 * `value` = algorithmic latent+scale bytes of all ranks / max-over-ranks device time.
+* `strong`: the two workloads that are head-sharded by definition (c3, c4) measured the
+  same way at this N (fewer steps); `triton_reference` (N = 1): the reference's own Triton
+  kernels on this GPU when baseline/_ref is present.
 * `e2e` = the same step through the public Python op with the per-step inputs (q and
   the batch metadata) copied from pinned host memory and the result copied back to the
   host inside the timed region; the latent KV cache is resident device state, as in the
@@ -40,9 +43,30 @@ sys.path.insert(0, ROOT)
 METRIC = "latent decode-attn µs/layer & achieved HBM GB/s (1/2/4/8 B200), 7B/13B shapes"
 DEFAULT_WORKLOAD = "c2_13b_b16_s8192"
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one stage-1 launch, from the ncu capture
-# summarised in profiles/latent_decode_stage1_tc_c2.md
-NCU_TRAFFIC_BYTES = {"c2_13b_b16_s8192": 711555328}
+# dram__bytes_read.sum + dram__bytes_write.sum of one stage-1 launch from an ncu capture, keyed by
+# workload: (bytes, sha256[:12] of the stage-1 kernel source the capture was taken with).  The
+# number is reported only while the kernel source is unchanged; otherwise `traffic` is null.
+NCU_TRAFFIC = {}
+STAGE1_SOURCE = os.path.join(ROOT, "wsvd_b200", "csrc", "latent_decode_tc_sm100.cu")
+
+
+def stage1_source_tag():
+    import hashlib
+
+    try:
+        with open(STAGE1_SOURCE, "rb") as f:
+            return hashlib.sha256(f.read()).hexdigest()[:12]
+    except OSError:
+        return None
+
+
+def ncu_traffic(workload):
+    hit = NCU_TRAFFIC.get(workload)
+    if hit is None or hit[1] != stage1_source_tag():
+        return None
+    return hit[0]
+
+
 C5_WORKLOAD = "c5_7b_b64_s4096_step"
 
 
@@ -130,20 +154,33 @@ def cpu_reference_run(spec, steps, warmup, sample_batch=2):
     }
 
 
+def workload_config(spec, heads_per_gpu, world):
+    """What identifies the workload; both arms print exactly this dict."""
+    from wsvd_b200 import inputs
+
+    nbytes = inputs.algorithmic_bytes(inputs.seq_lens_for(spec), heads_per_gpu, spec.rank_k, spec.rank_v)
+    return {"workload": spec.name, "batch": spec.batch, "heads": spec.heads, "heads_per_gpu": heads_per_gpu,
+            "head_dim": spec.head_dim, "rank_k": spec.rank_k, "rank_v": spec.rank_v, "context": spec.max_len,
+            "parallelism": f"heads x{world}",
+            "l2": (f"{nbytes / 1e6:.0f} MB of latents+scales per GPU per step, larger than the 126 MB L2"
+                   if nbytes >= (300 << 20) else
+                   f"{nbytes / 1e6:.0f} MB of latents+scales per GPU per step would fit the 126 MB L2: a 512 MB "
+                   "buffer is written before every timed call")}
+
+
 def run_reference(args, spec):
+    """The reference arm: the reference's CPU-runnable path on the host cores, `--steps` timed
+    steps after `--warmup` untimed ones, each step a bounded sample of the workload."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 10))
-    warm = max(1, min(args.warmup, 2))
-    cb = cpu_reference_run(spec, steps, warm)
+    cb = cpu_reference_run(spec, args.steps, max(args.warmup, 1), sample_batch=1)
     line = {
         "impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "GB/s", "n_gpus": args.gpus,
-        "steps": steps, "warmup": warm, "ms_per_step": cb["ms_per_step_sample"], "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "i8 latents, f32 math", "data": "synthetic",
-        "config": {"workload": spec.name, "batch": spec.batch, "heads": spec.heads, "head_dim": spec.head_dim,
-                   "rank_k": spec.rank_k, "rank_v": spec.rank_v, "context": spec.max_len,
-                   "l2": "CPU run; sample larger than the host caches"},
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["ms_per_step_sample"], "higher_is_better": True,
+        "scaling": "strong" if args.gpus > 1 and not args.weak else "weak", "vs_baseline": None,
+        "dtype": "i8 latents, f32 math", "data": "synthetic",
+        "config": workload_config(spec, spec.heads // args.gpus if not args.weak else spec.heads, args.gpus),
         "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "us_per_layer_extrapolated": cb["us_per_layer_extrapolated"],
@@ -305,6 +342,218 @@ def run_c5(args):
         dist.destroy_process_group()
 
 
+class Measurement:
+    """One workload on this rank's head shard: the step, stage 1 alone, the end-to-end call."""
+
+    def __init__(self, args, spec, world, rank, dev, dist):
+        import ctypes
+
+        from wsvd_b200 import _lib, inputs, ops
+
+        self.args, self.spec, self.world, self.rank, self.dev, self.dist = args, spec, world, rank, dev, dist
+        self.ct, self._lib, self.ops, self.inputs = ctypes, _lib, ops, inputs
+        self.strong = world > 1 and not args.weak
+        if self.strong:
+            if spec.heads % world:
+                raise SystemExit(f"{spec.heads} heads do not divide over {world} ranks")
+            per = spec.heads // world
+            self.case = inputs.make_workload(spec, device=dev, heads=slice(rank * per, (rank + 1) * per))
+        elif world > 1:
+            shard_spec = inputs.WorkloadSpec(**{**spec.__dict__, "seed": spec.seed + 7919 * rank})
+            self.case = inputs.make_workload(shard_spec, device=dev)
+        else:
+            self.case = inputs.make_workload(spec, device=dev)
+        case = self.case
+        st = case.infer_state
+        self.B, self.H, self.D = case.q.shape
+        self.lens = case.seq_lens
+        self.bytes_rank = inputs.algorithmic_bytes(self.lens, self.H, spec.rank_k, spec.rank_v)
+        self.bytes_total = self.bytes_rank * world
+        self.out = torch.empty(self.B, self.H, self.D, dtype=torch.float16, device=dev)
+        self.gathered = (torch.empty(world, self.B, self.H, self.D, dtype=torch.float16, device=dev)
+                         if world > 1 else None)
+        self.p, self._keep = ops.build_params(case.q, st.b_seq_len, st.b_req_idx, st.req_manager.req_to_token_indexs,
+                                              st.max_len_in_batch, case.latent_k, case.k_scale, case.latent_v,
+                                              case.v_scale, case.wk, None, wv=case.wv, out=self.out,
+                                              split_len=args.split_len, kernel=args.kernel)
+        self.split_len, self.n_splits = ops.plan(self.p)
+        self.ws = torch.empty((ops.workspace_bytes(self.p) + 3) // 4, dtype=torch.float32, device=dev)
+        self.stream = torch.cuda.current_stream()
+        self.lib = _lib.lib()
+        # N>1: the path's one exchange, the all-gather of the heads.  "fused": the merge kernel of
+        # every rank stores its rows into all ranks' gathered buffers and runs the group barrier
+        # (wsvd_latent_decode_gather); "nccl": the plain library collective after the op.
+        self.pg, self.collective = None, "none"
+        if world > 1:
+            self.collective = "nccl all_gather of [B,H_local,128] f16"
+            if args.collective == "fused":
+                from wsvd_b200.dist import PeerGather
+                ok = torch.ones(1, device=dev)
+                try:
+                    self.pg = PeerGather(self.B, self.H * world, self.D, device=dev, timeout_ms=10000)
+                except Exception as exc:  # no peer mapping on this box: say so and use the library collective
+                    print(f"[bench] rank {rank}: peer buffers unavailable ({exc}); using NCCL", file=sys.stderr)
+                    ok.zero_()
+                dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+                if ok.item() == 0:
+                    self.pg = None
+                else:
+                    self.collective = "fused into the merge kernel: peer stores of [B,H_local,128] f16 + flag barrier"
+        # inputs smaller than ~2x the 126 MB L2 would be served from cache on repeated calls:
+        # then every timed call is preceded by a write of a 512 MB buffer and timed on its own
+        self.flush = (torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+                      if self.bytes_rank < (300 << 20) else None)
+
+    # ---- the step
+    def step(self):
+        ct = self.ct
+        if self.pg is not None:
+            ps, _parity = self.pg.peer_set()
+            self._lib.check(self.lib.wsvd_latent_decode_gather(
+                ct.byref(self.p), ct.byref(ps), ct.c_void_p(self.ws.data_ptr()), self.ws.numel() * 4,
+                ct.c_void_p(self.stream.cuda_stream)), "wsvd_latent_decode_gather")
+            return
+        self._lib.check(self.lib.wsvd_latent_decode(ct.byref(self.p), ct.c_void_p(self.ws.data_ptr()),
+                                                    self.ws.numel() * 4, ct.c_void_p(self.stream.cuda_stream)),
+                        "wsvd_latent_decode")
+        if self.world > 1:
+            self.dist.all_gather_into_tensor(self.gathered, self.out)
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(self, fn, k):
+        """k calls bracketed by barrier+synchronize; device time by CUDA events, max over ranks."""
+        self.barrier()
+        if self.flush is None:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(k):
+                fn()
+            e1.record()
+            self.barrier()
+            total = e0.elapsed_time(e1)
+        else:
+            evs = []
+            for _ in range(k):
+                self.flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                evs.append((e0, e1))
+            self.barrier()
+            total = sum(a.elapsed_time(b) for a, b in evs)
+        ms = torch.tensor([total], device=self.dev)
+        if self.world > 1:
+            self.dist.all_reduce(ms, op=self.dist.ReduceOp.MAX)
+        return ms.item()
+
+    def time_step(self, steps, warmup):
+        for _ in range(warmup):
+            self.step()
+        return self.timed(self.step, steps) / steps
+
+    def time_graph(self, steps):
+        """The same step replayed from a CUDA graph (one GPU): what a serving loop that captures
+        its decode step pays; matters for the small workloads, which are bound by launch latency."""
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        keep = self.stream
+        with torch.cuda.graph(g):
+            self.stream = torch.cuda.current_stream()  # step() launches on the capturing stream
+            self.step()
+        self.stream = keep
+        for _ in range(3):
+            g.replay()
+        return self.timed(g.replay, steps) / steps
+
+    def time_stage1(self, steps):
+        """The dominant kernel alone (stage 1), for the roofline."""
+        ct, case, spec = self.ct, self.case, self.spec
+        st = case.infer_state
+        n = self.B * self.H * self.n_splits * spec.rank_v
+        mid_o, lse = self.ws[:n], self.ws[n:]
+        p1, self._k1 = self.ops.build_params(case.q, st.b_seq_len, st.b_req_idx, st.req_manager.req_to_token_indexs,
+                                             st.max_len_in_batch, case.latent_k, case.k_scale, case.latent_v,
+                                             case.v_scale, case.wk, None, split_len=self.split_len,
+                                             kernel=self.args.kernel)
+
+        def stage1():
+            self._lib.check(self.lib.wsvd_latent_decode_stage1(
+                ct.byref(p1), ct.c_void_p(mid_o.data_ptr()), ct.c_void_p(lse.data_ptr()), self.n_splits,
+                ct.c_void_p(self.stream.cuda_stream)), "stage1")
+
+        for _ in range(3):
+            stage1()
+        return self.timed(stage1, steps) / steps
+
+    def gather_check(self):
+        """Once, outside the timed region: the buffer the fused gather filled on this rank against
+        an NCCL all-gather of every rank's local output.  True when they are identical on all ranks."""
+        if self.world == 1 or self.pg is None:
+            return None
+        ct = self.ct
+        ps, parity = self.pg.peer_set()
+        self._lib.check(self.lib.wsvd_latent_decode_gather(
+            ct.byref(self.p), ct.byref(ps), ct.c_void_p(self.ws.data_ptr()), self.ws.numel() * 4,
+            ct.c_void_p(self.stream.cuda_stream)), "wsvd_latent_decode_gather")
+        fused = self.pg.buffer(parity).clone()
+        self._lib.check(self.lib.wsvd_latent_decode(ct.byref(self.p), ct.c_void_p(self.ws.data_ptr()),
+                                                    self.ws.numel() * 4, ct.c_void_p(self.stream.cuda_stream)),
+                        "wsvd_latent_decode")
+        self.dist.all_gather_into_tensor(self.gathered, self.out)
+        want = self.gathered.permute(1, 0, 2, 3).reshape(self.B, self.world * self.H, self.D)
+        same = torch.tensor([1.0 if torch.equal(fused, want) else 0.0], device=self.dev)
+        self.dist.all_reduce(same, op=self.dist.ReduceOp.MIN)
+        return bool(same.item() == 1.0)
+
+    def time_e2e(self, steps, op):
+        """End to end through the public op: host buffers in, host result out, every step."""
+        case, st, dev = self.case, self.case.infer_state, self.dev
+        B, H, D, world, pg, args = self.B, self.H, self.D, self.world, self.pg, self.args
+        q_host = case.q.cpu().pin_memory()
+        len_host = st.b_seq_len.cpu().pin_memory()
+        req_host = st.b_req_idx.cpu().pin_memory()
+        # (with the fused gather the step's result is the gathered [B, H_total, D] buffer)
+        out_host = torch.empty(B, H * (world if pg is not None else 1), D, dtype=torch.float16).pin_memory()
+        q_dev, len_dev, req_dev = (torch.empty_like(case.q), torch.empty_like(st.b_seq_len),
+                                   torch.empty_like(st.b_req_idx))
+        from wsvd_b200.infer_state import InferState
+        st2 = InferState(B, st.max_len_in_batch, self.lens, device=dev, req_to_token=st.req_manager.req_to_token_indexs)
+        st2.b_seq_len, st2.b_req_idx = len_dev, req_dev
+
+        def e2e_step():
+            q_dev.copy_(q_host, non_blocking=True)
+            len_dev.copy_(len_host, non_blocking=True)
+            req_dev.copy_(req_host, non_blocking=True)
+            if pg is not None:
+                o = pg.decode(q_dev, st2, case.latent_k, case.k_scale, case.latent_v, case.v_scale, case.wk, None,
+                              wv=case.wv, workspace=self.ws, split_len=args.split_len, kernel=args.kernel)
+            else:
+                o = op(q_dev, st2, H, D, case.latent_k, case.k_scale, case.latent_v, case.v_scale, case.wk, None,
+                       wv=case.wv, out=self.out, workspace=self.ws, split_len=args.split_len, kernel=args.kernel)
+                if world > 1:
+                    self.dist.all_gather_into_tensor(self.gathered, o)
+            out_host.copy_(o, non_blocking=True)
+            torch.cuda.current_stream().synchronize()  # the caller consumes the host result every step
+
+        for _ in range(3):
+            e2e_step()
+        ms = self.timed(e2e_step, steps) / steps
+        h2d = q_host.numel() * 2 + len_host.numel() * 4 + req_host.numel() * 4
+        return ms, h2d, out_host.numel() * 2
+
+    def close(self):
+        if self.pg is not None:
+            self.pg.close()
+            self.pg = None
+        self.case = self.ws = self.flush = self.out = self.gathered = self._keep = None
+        torch.cuda.empty_cache()
+
+
 def main():
     # NCCL writes its version banner to stdout at NCCL_DEBUG=VERSION; stdout is for the one JSON line
     if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
@@ -318,13 +567,18 @@ def main():
     ap.add_argument("--kernel", default="auto", choices=["auto", "generic", "tc"])
     ap.add_argument("--split-len", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--shard-heads", action="store_true",
-                    help="N>1: divide the workload's heads over the ranks (strong scaling) instead of giving "
-                         "every rank a full-size shard (weak scaling, the default)")
+    ap.add_argument("--weak", action="store_true",
+                    help="N>1: give every rank a full-size shard of its own (weak scaling) instead of dividing the "
+                         "workload's heads over the ranks (strong scaling, the default)")
+    ap.add_argument("--shard-heads", action="store_true", help="accepted for compatibility: strong scaling is the default")
     ap.add_argument("--no-graph", action="store_true", help="c5 step: launch from Python instead of one CUDA graph")
     ap.add_argument("--collective", default="fused", choices=["fused", "nccl"],
                     help="N>1: head all-gather fused into the merge kernel (peer stores), or an NCCL all_gather")
     ap.add_argument("--no-dense", action="store_true", help="skip the dense f16 baseline kernel timing")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="skip the `strong` list (c3, c4 at this N) and the reference Triton kernels")
+    ap.add_argument("--triton-reference", action="store_true",
+                    help="only time the reference's Triton kernels (baseline/_ref) on this GPU and print their line")
     args = ap.parse_args()
 
     from wsvd_b200 import inputs
@@ -337,9 +591,7 @@ def main():
         run_reference(args, spec)
         return
 
-    import ctypes
-
-    from wsvd_b200 import _lib, ops
+    from wsvd_b200 import ops
     from wsvd_b200.kernel.flash_decoding import token_decode_attention_flash_int8_latent_per_head_decoding_rope as op
 
     if not torch.cuda.is_available():
@@ -351,242 +603,143 @@ def main():
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch N>1 under torch.distributed.run")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    if args.triton_reference:
+        print(json.dumps({"impl": "reference-triton", "n_gpus": 1, **triton_reference_leg(spec, dev, op, args)}),
+              flush=True)
+        return
     dist = None
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
     args.warmup = max(args.warmup, 3)
+    peak, peak_kind = measured_peaks()
 
-    # ---- workload: this rank's head shard, generated on the device ----
-    if args.shard_heads and world > 1:
-        # strong scaling: the named workload's heads are divided over the ranks
-        if spec.heads % world:
-            raise SystemExit(f"{spec.heads} heads do not divide over {world} ranks")
-        per = spec.heads // world
-        case = inputs.make_workload(spec, device=dev, heads=slice(rank * per, (rank + 1) * per))
-    else:
-        shard_spec = inputs.WorkloadSpec(**{**spec.__dict__, "seed": spec.seed + 7919 * rank})
-        case = inputs.make_workload(shard_spec, device=dev)
-    st = case.infer_state
-    B, H, D = case.q.shape
-    lens = case.seq_lens
-    bytes_rank = inputs.algorithmic_bytes(lens, H, spec.rank_k, spec.rank_v)
-    bytes_total = bytes_rank * world
-    out = torch.empty(B, H, D, dtype=torch.float16, device=dev)
-    gathered = torch.empty(world, B, H, D, dtype=torch.float16, device=dev) if world > 1 else None
-    p, _keep = ops.build_params(case.q, st.b_seq_len, st.b_req_idx, st.req_manager.req_to_token_indexs,
-                                st.max_len_in_batch, case.latent_k, case.k_scale, case.latent_v, case.v_scale,
-                                case.wk, None, wv=case.wv, out=out, split_len=args.split_len, kernel=args.kernel)
-    split_len, n_splits = ops.plan(p)
-    ws = torch.empty((ops.workspace_bytes(p) + 3) // 4, dtype=torch.float32, device=dev)
-    stream = torch.cuda.current_stream()
-    lib = _lib.lib()
-
-    # N>1: the path's one exchange, the all-gather of the heads.  "fused": the merge kernel of
-    # every rank stores its rows into all ranks' gathered buffers and runs the group barrier
-    # (wsvd_latent_decode_gather); "nccl": the plain library collective after the op.
-    pg, collective = None, "none"
-    if world > 1:
-        collective = "nccl all_gather of [B,H_local,128] f16"
-        if args.collective == "fused":
-            from wsvd_b200.dist import PeerGather
-            ok = torch.ones(1, device=dev)
-            try:
-                pg = PeerGather(B, H * world, D, device=dev, timeout_ms=10000)
-            except Exception as exc:  # no peer mapping on this box: say so and use the library collective
-                print(f"[bench] rank {rank}: peer buffers unavailable ({exc}); using NCCL", file=sys.stderr)
-                ok.zero_()
-            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-            if ok.item() == 0:
-                pg = None
-            else:
-                collective = "fused into the merge kernel: peer stores of [B,H_local,128] f16 + flag barrier"
-
-    def step():
-        if pg is not None:
-            ps, _parity = pg.peer_set()
-            _lib.check(lib.wsvd_latent_decode_gather(ctypes.byref(p), ctypes.byref(ps), ctypes.c_void_p(ws.data_ptr()),
-                                                     ws.numel() * 4, ctypes.c_void_p(stream.cuda_stream)),
-                       "wsvd_latent_decode_gather")
-            return
-        _lib.check(lib.wsvd_latent_decode(ctypes.byref(p), ctypes.c_void_p(ws.data_ptr()), ws.numel() * 4,
-                                          ctypes.c_void_p(stream.cuda_stream)), "wsvd_latent_decode")
-        if world > 1:
-            dist.all_gather_into_tensor(gathered, out)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    # inputs smaller than ~2x the 126 MB L2 would be served from cache on repeated calls:
-    # then every timed call is preceded by a write of a 512 MB buffer and timed on its own
-    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev) if bytes_rank < (300 << 20) else None
-
-    def timed(fn, k):
-        """k calls bracketed by barrier+synchronize; device time by CUDA events, max over ranks."""
-        barrier()
-        if flush is None:
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(k):
-                fn()
-            e1.record()
-            barrier()
-            total = e0.elapsed_time(e1)
-        else:
-            evs = []
-            for _ in range(k):
-                flush.zero_()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record()
-                fn()
-                e1.record()
-                evs.append((e0, e1))
-            barrier()
-            total = sum(a.elapsed_time(b) for a, b in evs)
-        ms = torch.tensor([total], device=dev)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return ms.item()
-
+    m = Measurement(args, spec, world, rank, dev, dist)
     for _ in range(args.warmup):
-        step()
+        m.step()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    ms_total = timed(step, args.steps)
-    ms_step = ms_total / args.steps
-
-    # ---- the same step replayed from a CUDA graph (one GPU): what a serving loop that captures its
-    #      decode step pays; matters for the small workloads, which are bound by launch latency ----
-    ms_graph = None
-    if world == 1:
-        torch.cuda.synchronize()
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            stream = torch.cuda.current_stream()  # step() launches on `stream`
-            step()
-        stream = torch.cuda.current_stream()
-        for _ in range(3):
-            g.replay()
-        ms_graph = timed(g.replay, args.steps) / args.steps
-
-    # ---- dominant kernel alone (stage 1), for the roofline ----
-    mid_o = ws[: B * H * n_splits * spec.rank_v]
-    lse = ws[B * H * n_splits * spec.rank_v:]
-    p1, _k1 = ops.build_params(case.q, st.b_seq_len, st.b_req_idx, st.req_manager.req_to_token_indexs,
-                               st.max_len_in_batch, case.latent_k, case.k_scale, case.latent_v, case.v_scale,
-                               case.wk, None, split_len=split_len, kernel=args.kernel)
-
-    def stage1():
-        _lib.check(lib.wsvd_latent_decode_stage1(ctypes.byref(p1), ctypes.c_void_p(mid_o.data_ptr()),
-                                                 ctypes.c_void_p(lse.data_ptr()), n_splits,
-                                                 ctypes.c_void_p(stream.cuda_stream)), "stage1")
-
-    for _ in range(3):
-        stage1()
-    ms_stage1 = timed(stage1, args.steps) / args.steps
-
-    # ---- end to end through the public op, host buffers in, host result out ----
-    q_host = case.q.cpu().pin_memory()
-    len_host = st.b_seq_len.cpu().pin_memory()
-    req_host = st.b_req_idx.cpu().pin_memory()
-    # (with the fused gather the step's result is the gathered [B, H_total, D] buffer)
-    out_host = torch.empty(B, H * (world if pg is not None else 1), D, dtype=torch.float16).pin_memory()
-    q_dev, len_dev, req_dev = torch.empty_like(case.q), torch.empty_like(st.b_seq_len), torch.empty_like(st.b_req_idx)
-    from wsvd_b200.infer_state import InferState
-    st2 = InferState(B, st.max_len_in_batch, lens, device=dev, req_to_token=st.req_manager.req_to_token_indexs)
-    st2.b_seq_len, st2.b_req_idx = len_dev, req_dev
-
-    def e2e_step():
-        q_dev.copy_(q_host, non_blocking=True)
-        len_dev.copy_(len_host, non_blocking=True)
-        req_dev.copy_(req_host, non_blocking=True)
-        if pg is not None:
-            o = pg.decode(q_dev, st2, case.latent_k, case.k_scale, case.latent_v, case.v_scale, case.wk, None,
-                          wv=case.wv, workspace=ws, split_len=args.split_len, kernel=args.kernel)
-        else:
-            o = op(q_dev, st2, H, D, case.latent_k, case.k_scale, case.latent_v, case.v_scale, case.wk, None,
-                   wv=case.wv, out=out, workspace=ws, split_len=args.split_len, kernel=args.kernel)
-            if world > 1:
-                dist.all_gather_into_tensor(gathered, o)
-        out_host.copy_(o, non_blocking=True)
-        torch.cuda.current_stream().synchronize()  # the caller consumes the host result every step
-
-    for _ in range(3):
-        e2e_step()
-    ms_e2e = timed(e2e_step, args.steps) / args.steps
+    ms_step = m.timed(m.step, args.steps) / args.steps
+    ms_graph = m.time_graph(args.steps) if world == 1 else None
+    ms_stage1 = m.time_stage1(args.steps)
+    ms_e2e, h2d, d2h = m.time_e2e(args.steps, op)
     clocks = sampler.stop() if rank == 0 else None
+    gather_ok = m.gather_check()
     status = torch.tensor([ops.kernel_status()], device=dev)
     if world > 1:
         dist.all_reduce(status, op=dist.ReduceOp.MAX)
-    h2d = q_host.numel() * 2 + len_host.numel() * 4 + req_host.numel() * 4
-    d2h = out_host.numel() * 2
 
+    line = None
     if rank == 0:
-        peak, peak_kind = measured_peaks()
-        achieved = bytes_rank / (ms_stage1 * 1e-3) / 1e9
+        achieved = m.bytes_rank / (ms_stage1 * 1e-3) / 1e9
         line = {
-            "metric": METRIC, "value": bytes_total / (ms_step * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world,
+            "metric": METRIC, "value": m.bytes_total / (ms_step * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "us_per_layer": ms_step * 1e3,
             "us_per_layer_cuda_graph": None if ms_graph is None else ms_graph * 1e3,
-            "higher_is_better": True, "scaling": "strong" if args.shard_heads and world > 1 else "weak",
+            "higher_is_better": True, "scaling": "strong" if m.strong or world == 1 else "weak",
             "vs_baseline": None,
             "dtype": "i8 latents, f16 tensor-core operands, f32 accumulate/softmax", "data": "synthetic",
-            "config": {
-                "workload": spec.name, "batch": spec.batch, "heads_per_gpu": H, "head_dim": D,
-                "rank_k": spec.rank_k, "rank_v": spec.rank_v, "context": spec.max_len, "split_len": split_len,
-                "n_splits": n_splits, "kernel": args.kernel, "parallelism": f"heads x{world}",
-                "collective": collective,
-                "l2": (f"inputs {bytes_rank / 1e6:.0f} MB per GPU, larger than the 126 MB L2" if flush is None else
-                       f"inputs {bytes_rank / 1e6:.0f} MB per GPU fit L2: a 512 MB buffer is written before every "
-                       "timed call"),
-            },
+            "config": workload_config(spec, m.H, world),
+            "plan": {"split_len": m.split_len, "n_splits": m.n_splits, "kernel": args.kernel,
+                     "collective": m.collective},
             "roofline": {
                 "bound": "hbm", "kernel": "latent decode stage 1", "achieved": achieved, "peak": peak,
                 "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
-                "us_per_launch": ms_stage1 * 1e3, "algorithmic_bytes_per_launch": bytes_rank,
-                "traffic": NCU_TRAFFIC_BYTES.get(spec.name),
+                "us_per_launch": ms_stage1 * 1e3, "algorithmic_bytes_per_launch": m.bytes_rank,
+                "traffic": ncu_traffic(spec.name),
             },
-            "e2e": {"value": bytes_total / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "us_per_layer": ms_e2e * 1e3,
+            # what the merge (and, at N>1, the fused exchange with its group barrier) adds to stage 1
+            "us_merge_gather": (ms_step - ms_stage1) * 1e3,
+            "gather_check": gather_ok,
+            "e2e": {"value": m.bytes_total / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "us_per_layer": ms_e2e * 1e3,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": args.steps * 2,
             "kernel_status": int(status.item()),
             "clocks": clocks,
         }
         if world == 1 and not args.no_dense:
-            # dense f16 flash-decoding of the same shape (K/V [T,H,128] f16, 512 B per token-head)
-            from wsvd_b200.infer_state import InferState as _IS
-            from wsvd_b200.kernel.flash_decoding import token_decode_attention_flash_decoding as dense_op
-            S = spec.max_len
-            kd = torch.randn(B, H, S, D, dtype=torch.float16, device=dev)
-            vd = torch.randn(B, H, S, D, dtype=torch.float16, device=dev)
-            kv = kd.as_strided(((B - 1) * H * S + S, H, D), (D, S * D, 1))
-            vv = vd.as_strided(((B - 1) * H * S + S, H, D), (D, S * D, 1))
-            dst = _IS(B, S, lens, device=dev, req_to_token=st.req_manager.req_to_token_indexs)
-            dout = torch.empty(B, H, D, dtype=torch.float16, device=dev)
-            dws = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
-            dense = lambda: dense_op(case.q, dst, H, D, kv, vv, out=dout, workspace=dws)
-            for _ in range(3):
-                dense()
-            ms_dense = timed(dense, max(5, args.steps // 2)) / max(5, args.steps // 2)
-            dense_bytes = sum(lens) * H * 4 * D
-            line["dense_f16_baseline"] = {
-                "us_per_layer": ms_dense * 1e3, "GB/s": dense_bytes / (ms_dense * 1e-3) / 1e9,
-                "bytes_per_token_head": 4 * D, "latent_speedup": ms_dense / ms_step,
-                "byte_reduction": 4 * D / (spec.rank_k + spec.rank_v + 4)}
-            del kd, vd
-        if world == 1 and not args.no_cpu_baseline:
-            cb = cpu_reference_run(spec, steps=3, warmup=1)
-            line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
-            line["cpu_baseline"]["us_per_layer_extrapolated"] = cb["us_per_layer_extrapolated"]
+            line["dense_f16_baseline"] = dense_baseline(m, spec, ms_step, max(5, args.steps // 2))
+    m.close()
+
+    # ---- the head-sharded workloads (c3, c4) at this N, fewer steps ----
+    if not args.no_extra and spec.name == DEFAULT_WORKLOAD:
+        strong = []
+        for name in ("c3_next7b_b32_ragged4096", "c4_13b_b64_ragged32k"):
+            xs = inputs.WORKLOADS[name]
+            if xs.heads % world:
+                continue
+            k = max(5, min(20, args.steps // 2))
+            mx = Measurement(args, xs, world, rank, dev, dist)
+            ms_x = mx.time_step(k, 3)
+            ms_x1 = mx.time_stage1(k)
+            ok_x = mx.gather_check()
+            if rank == 0:
+                strong.append({
+                    "workload": name, "heads_per_gpu": mx.H, "split_len": mx.split_len, "n_splits": mx.n_splits,
+                    "steps": k, "us_per_layer": ms_x * 1e3, "GB/s": mx.bytes_total / (ms_x * 1e-3) / 1e9,
+                    "us_stage1": ms_x1 * 1e3, "stage1_frac_per_gpu": mx.bytes_rank / (ms_x1 * 1e-3) / 1e9 / peak,
+                    "gather_check": ok_x})
+            mx.close()
+        if rank == 0:
+            line["strong"] = strong
+    if rank == 0 and world == 1 and not args.no_extra:
+        line["triton_reference"] = triton_reference_leg(spec, dev, op, args)
+        ref_dense = line["triton_reference"].get("triton_dense_f16")
+        if ref_dense:
+            line["triton_reference"]["latent_speedup_vs_reference_dense"] = ref_dense["us_per_layer"] / (ms_step * 1e3)
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cb = cpu_reference_run(spec, steps=3, warmup=1)
+        line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        line["cpu_baseline"]["us_per_layer_extrapolated"] = cb["us_per_layer_extrapolated"]
+    if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
-        if pg is not None:
-            pg.close()
         dist.barrier()
         dist.destroy_process_group()
+
+
+def dense_baseline(m, spec, ms_step, k):
+    """This library's dense f16 flash-decoding kernel on the same shape (K/V [T,H,128] f16, 512 B
+    per token-head)."""
+    from wsvd_b200.infer_state import InferState
+    from wsvd_b200.kernel.flash_decoding import token_decode_attention_flash_decoding as dense_op
+
+    B, H, D, dev, S = m.B, m.H, m.D, m.dev, spec.max_len
+    st = m.case.infer_state
+    kd = torch.randn(B, H, S, D, dtype=torch.float16, device=dev)
+    vd = torch.randn(B, H, S, D, dtype=torch.float16, device=dev)
+    kv = kd.as_strided(((B - 1) * H * S + S, H, D), (D, S * D, 1))
+    vv = vd.as_strided(((B - 1) * H * S + S, H, D), (D, S * D, 1))
+    dst = InferState(B, S, m.lens, device=dev, req_to_token=st.req_manager.req_to_token_indexs)
+    dout = torch.empty(B, H, D, dtype=torch.float16, device=dev)
+    dws = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
+    dense = lambda: dense_op(m.case.q, dst, H, D, kv, vv, out=dout, workspace=dws)
+    for _ in range(3):
+        dense()
+    ms_dense = m.timed(dense, k) / k
+    dense_bytes = sum(m.lens) * H * 4 * D
+    return {"us_per_layer": ms_dense * 1e3, "GB/s": dense_bytes / (ms_dense * 1e-3) / 1e9,
+            "bytes_per_token_head": 4 * D, "latent_speedup": ms_dense / ms_step,
+            "byte_reduction": 4 * D / (spec.rank_k + spec.rank_v + 4)}
+
+
+def triton_reference_leg(spec, dev, op, args):
+    """The reference's Triton kernels on this GPU (baseline/_ref), or why they cannot run."""
+    try:
+        from baseline import triton_reference as tr
+    except Exception as exc:
+        return {"unavailable": f"baseline/triton_reference.py cannot be imported: {exc}"}
+
+    def ours(case):
+        s = case.infer_state
+        return op(case.q, s, case.q.shape[1], case.q.shape[2], case.latent_k, case.k_scale, case.latent_v,
+                  case.v_scale, case.wk, None, kernel=args.kernel)
+
+    try:
+        return tr.run(spec, dev, steps=max(5, min(20, args.steps)), warmup=3, ours=ours)
+    except Exception as exc:  # the reference's code failed here: report it, keep this library's line
+        return {"unavailable": f"the reference kernels raised {type(exc).__name__}: {exc}"[:300]}
 
 
 if __name__ == "__main__":

@@ -67,6 +67,9 @@ def unpack_wk(wk: torch.Tensor, wk_scale: Optional[torch.Tensor], n_kv_heads: in
     return w.reshape(r, n_kv_heads, head_dim).permute(1, 2, 0).contiguous()
 
 
+F16_TINY, F16_MAX = 2.0 ** -24, 65504.0  # smallest positive (subnormal) and largest finite f16
+
+
 def quantize_per_token(x: torch.Tensor, bits: int = 8) -> Tuple[torch.Tensor, torch.Tensor]:
     """Symmetric per-(token, head) int8 quantisation over the last dim.
 
@@ -80,7 +83,9 @@ def quantize_per_token(x: torch.Tensor, bits: int = 8) -> Tuple[torch.Tensor, to
     amax = xf.abs().amax(dim=-1)
     scale = amax / maxq
     scale = torch.where(amax == 0, torch.ones_like(scale), scale)
-    scale_h = scale.to(torch.float16)
+    # the cache stores the scale as f16: keep it a usable divisor when amax/maxq leaves the
+    # f16 range (the reference keeps the scale in the input dtype, quant_utils.py:175-184)
+    scale_h = scale.clamp(min=F16_TINY, max=F16_MAX).to(torch.float16)
     # an f16 scale that rounded down could push round(x/scale) to maxq+1; the clamp
     # keeps it in range exactly as the reference's clamp does
     q = torch.clamp(torch.round(xf / scale_h.float().unsqueeze(-1)), -(maxq + 1), maxq)

@@ -61,6 +61,23 @@ def test_validation_status_codes(field, value, status):
     assert lib.wsvd_latent_decode(ctypes.byref(p), ws, 1 << 30, None) == status
 
 
+@pytest.mark.parametrize("batch", [0, 2])
+@pytest.mark.parametrize("field,value,status", [("q", None, 1), ("head_dim", 96, 2), ("latent_dtype", 7, 3)])
+def test_static_entry_validates_like_the_workspace_entry(batch, field, value, status):
+    """An invalid argument block is rejected by wsvd_latent_decode_static with the same code as
+    by wsvd_latent_decode, also when the batch is empty (and before any CUDA call)."""
+    lib = _lib.lib()
+    p = _params(batch=batch, **{field: value})
+    assert lib.wsvd_latent_decode(ctypes.byref(p), ctypes.c_void_p(0x2000), 1 << 30, None) == status
+    assert lib.wsvd_latent_decode_static(ctypes.byref(p), None) == status
+
+
+def test_static_entry_accepts_a_valid_empty_batch():
+    lib = _lib.lib()
+    p = _params(batch=0)
+    assert lib.wsvd_latent_decode_static(ctypes.byref(p), None) == 0
+
+
 def test_int8_wk_needs_scale_and_workspace_checks():
     lib = _lib.lib()
     p = _params(wk_dtype=0)

@@ -45,6 +45,15 @@ def test_oracle_append_writes_only_the_new_slots():
     assert torch.equal(lk[int(table[1, 5])], qk[1]) and torch.equal(ks[int(table[1, 5])], sk[1])
 
 
+def test_oracle_scale_stays_a_finite_nonzero_f16():
+    g = torch.Generator().manual_seed(9)
+    x = torch.stack([torch.randn(16, generator=g) * 2e-6, torch.randn(16, generator=g) * 3e7, torch.zeros(16)])
+    q, s = quantize_per_token(x)
+    assert torch.isfinite(s.float()).all() and (s.float() > 0).all()
+    assert s[2] == 1.0 and (q[2] == 0).all()
+    assert q[0].abs().max() > 0 and q[1].abs().max() == 127 or q[1].min() == -128
+
+
 class _Req:
     def __init__(self, t):
         self.req_to_token_indexs = t
@@ -72,6 +81,10 @@ def test_append_matches_oracle_bit_exact(dtype, B, H, Rk, Rv):
     xk = (torch.randn(B, H, Rk, generator=g) * torch.rand(B, H, 1, generator=g) * 4).to(dtype)
     xv = (torch.randn(B, H, Rv, generator=g) * 0.3).to(dtype)
     xk[0, 0] = 0  # all-zero row -> scale 1
+    # rows whose amax/127 leaves the f16 range: the stored scale is clamped, never 0 or inf
+    xk[1, 0] = (torch.randn(Rk, generator=g) * 2e-6).to(dtype)
+    if dtype == torch.float32:
+        xv[1, 0] = torch.randn(Rv, generator=g) * 3e7
     lk = torch.randint(-128, 128, (T, H, Rk), generator=g, dtype=torch.int8)
     lv = torch.randint(-128, 128, (T, H, Rv), generator=g, dtype=torch.int8)
     ks = torch.rand(T, H, generator=g).to(torch.float16)

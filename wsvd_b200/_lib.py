@@ -43,22 +43,39 @@ def _stale() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile every .cu under csrc/ into one shared object for sm_100a."""
+    """Compile every .cu under csrc/ into one shared object for sm_100a.
+
+    Safe when several processes start at once (one rank per GPU under torchrun): the
+    staleness check, the compile and the rename happen under an inter-process file lock, the
+    compiler writes to a per-process temporary name, and a process that gets the lock after
+    another one has built finds the library fresh and returns."""
+    import fcntl
+
     with _lock:
         if not force and not _stale():
             return LIB_PATH
-        nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
-        if not os.path.exists(nvcc):
-            raise RuntimeError("nvcc not found: cannot build libwsvd_b200.so")
-        cmd = [nvcc, *NVCC_FLAGS, "-I", _INCLUDE, "-I", _CSRC, *sources(), "-o", LIB_PATH + ".tmp", "-lcuda"]
-        if verbose:
-            cmd.insert(1, "-Xptxas=-v")
-        res = subprocess.run(cmd, capture_output=True, text=True)
-        if res.returncode != 0:
-            raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
-        if verbose:
-            print(res.stderr)
-        os.replace(LIB_PATH + ".tmp", LIB_PATH)
+        with open(LIB_PATH + ".lock", "w") as lockfile:
+            fcntl.flock(lockfile, fcntl.LOCK_EX)
+            try:
+                if not force and not _stale():
+                    return LIB_PATH
+                nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+                if not os.path.exists(nvcc):
+                    raise RuntimeError("nvcc not found: cannot build libwsvd_b200.so")
+                tmp = f"{LIB_PATH}.{os.getpid()}.tmp"
+                cmd = [nvcc, *NVCC_FLAGS, "-I", _INCLUDE, "-I", _CSRC, *sources(), "-o", tmp, "-lcuda"]
+                if verbose:
+                    cmd.insert(1, "-Xptxas=-v")
+                res = subprocess.run(cmd, capture_output=True, text=True)
+                if res.returncode != 0:
+                    if os.path.exists(tmp):
+                        os.remove(tmp)
+                    raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
+                if verbose:
+                    print(res.stderr)
+                os.replace(tmp, LIB_PATH)
+            finally:
+                fcntl.flock(lockfile, fcntl.LOCK_UN)
         return LIB_PATH
 
 

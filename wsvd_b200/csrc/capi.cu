@@ -134,6 +134,11 @@ size_t partial_bytes(const WsvdLatentDecodeParams* p, int ns) {
 
 }  // namespace
 
+namespace wsvd {
+int record_cuda_error(cudaError_t e) { return cuda_fail(e); }
+int validate_decode_params(const WsvdLatentDecodeParams* p) { return validate(p, true); }
+}  // namespace wsvd
+
 extern "C" {
 
 int wsvd_abi_version(void) { return WSVD_ABI_VERSION; }

@@ -18,6 +18,7 @@ namespace wsvd {
 namespace {
 
 constexpr int kThreads = 128;
+constexpr int kMaxOutRow = 1024;  // widest output row (head_dim) the entry points accept
 constexpr unsigned int kPeerWaitTimedOut = 6;
 __device__ unsigned int g_peer_status = 0;
 
@@ -62,12 +63,14 @@ stage2_kernel(const float* __restrict__ mid_o, const float* __restrict__ lse, co
     o /= wsum;
   }
   const int64_t doff = (int64_t)b * out_stride_b + (int64_t)(h + (kPeers ? pa.head_offset : 0)) * out_stride_h;
+  // With peers the finished row is staged in shared memory and leaves as 16-byte stores, one per
+  // thread per peer (a 128-dim row is 16 such stores per peer), instead of one 2-byte store per
+  // element per peer: NVLink carries far fewer, fuller packets.
+  __shared__ __align__(16) __half orow[kPeers ? kMaxOutRow : 8];
   auto store = [&](int d, float y) {
     const __half v = __float2half_rn(y);
     if constexpr (kPeers) {
-#pragma unroll
-      for (int i = 0; i < WSVD_MAX_PEERS; ++i)
-        if (i < pa.n_peers) pa.out[i][doff + d] = v;
+      orow[d] = v;
     } else {
       out[doff + d] = v;
     }
@@ -96,6 +99,22 @@ stage2_kernel(const float* __restrict__ mid_o, const float* __restrict__ lse, co
     }
   }
   if constexpr (kPeers) {
+    const int n_out = wv == nullptr ? width : head_dim;
+    __syncthreads();
+    bool vec = (n_out & 7) == 0 && (doff & 7) == 0;
+#pragma unroll
+    for (int i = 0; i < WSVD_MAX_PEERS; ++i)
+      if (i < pa.n_peers) vec = vec && (reinterpret_cast<uintptr_t>(pa.out[i]) & 15) == 0;
+    if (vec) {
+      const int chunks = n_out >> 3;
+      for (int idx = threadIdx.x; idx < chunks * pa.n_peers; idx += kThreads) {
+        const int peer = idx / chunks, c = idx - peer * chunks;
+        *reinterpret_cast<uint4*>(pa.out[peer] + doff + 8 * c) = reinterpret_cast<const uint4*>(orow)[c];
+      }
+    } else {
+      for (int d = threadIdx.x; d < n_out; d += kThreads)
+        for (int i = 0; i < pa.n_peers; ++i) pa.out[i][doff + d] = orow[d];
+    }
     // ---- group barrier, run by whichever block finishes last
     __shared__ bool last;
     __threadfence_system();  // this thread's peer stores are ordered before what follows

@@ -50,6 +50,12 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// Shared by the entry points that live outside capi.cu: the argument checks of
+// wsvd_latent_decode, and the per-thread record behind wsvd_last_cuda_error()
+// (returns WSVD_ERR_CUDA).
+int validate_decode_params(const WsvdLatentDecodeParams* p);
+int record_cuda_error(cudaError_t e);
+
 // Launchers implemented in the kernel translation units.
 cudaError_t launch_stage1_generic(const KArgs& a, cudaStream_t stream);
 cudaError_t launch_stage1_tc(const KArgs& a, const void* table, int table_rows, cudaStream_t stream);

@@ -79,17 +79,6 @@ enum Status : unsigned int { kOk = 0, kTimeoutProducer = 1, kTimeoutMma = 2, kTi
 
 __device__ unsigned int g_status = 0;
 
-// Optional cycle-stamp trace of one CTA (compile with -DWSVD_TC_TRACE): role x tile x event.
-#ifdef WSVD_TC_TRACE
-__device__ long long g_trace[8][64][8];
-#define WSVD_TRACE(role, t, ev)                                                         \
-  do {                                                                                  \
-    if (trace_cta && lane == 0 && (t) < 64) g_trace[role][t][ev] = clock64();          \
-  } while (0)
-#else
-#define WSVD_TRACE(role, t, ev)
-#endif
-
 // ------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -108,23 +97,13 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 // try_wait with a suspend-time hint: the waiting thread is parked by the hardware until
 // the phase completes or the hint (ns) expires, instead of spinning on issue slots that
 // the producer and MMA warps need.
-#ifndef WSVD_TC_WAIT_HINT_NS
-#define WSVD_TC_WAIT_HINT_NS 20000
-#endif
+constexpr uint32_t kWaitHintNs = 20000;
 __device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
-#ifdef WSVD_TC_TEST_WAIT
-  asm volatile(
-      "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok;
-#endif
   asm volatile(
       "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"((uint32_t)WSVD_TC_WAIT_HINT_NS)
+      : "r"(bar), "r"(parity), "r"(kWaitHintNs)
       : "memory");
   return ok;
 }
@@ -293,10 +272,6 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
   const int gqa = p.n_q_heads / p.n_kv_heads;
   const int Rv = p.rank_v;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#ifdef WSVD_TC_TRACE
-  const bool trace_cta = blockIdx.x == 1 && blockIdx.y == 1 && blockIdx.z == 1;
-  if (warp == 0) WSVD_TRACE(7, 0, 0);
-#endif
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t sbase = smem_u32(smem_raw);
@@ -398,7 +373,6 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  if (warp == 0) WSVD_TRACE(7, 0, 1);
 
   if (warp == kMmaWarp) {
     // ================================================================= table loads + MMA issue
@@ -419,7 +393,6 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       bool ok = mbar_wait(bar_pq, 0);
       for (int t = 0; t < ntiles && ok; ++t) {
         const int buf = t & 1;
-        WSVD_TRACE(1, t, 0);
         // The table tile of t+1 goes into the buffer MMA(t-1) read; that MMA was issued a
         // whole iteration ago, so this wait is short and the load overlaps MMA(t).
         if (t >= 1 && t + 1 < ntiles) {
@@ -428,9 +401,7 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
           issue_table(t + 1);
         }
         ok = mbar_wait(bar_a_full(buf), (t >> 1) & 1);
-        WSVD_TRACE(1, t, 1);
         if (ok && t >= 2) ok = mbar_wait(bar_w_empty(buf), ((t >> 1) - 1) & 1);
-        WSVD_TRACE(1, t, 2);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem + buf * (kG * kRk);
@@ -443,7 +414,6 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
         }
         umma_commit(bar_w_full(buf));
         umma_commit(bar_a_empty(buf));
-        WSVD_TRACE(1, t, 3);
       }
       if (!ok) atomicMax(&g_status, (unsigned)kTimeoutMma);
     }
@@ -652,7 +622,6 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_pq);
     }
-    if (warp == 0) WSVD_TRACE(7, 0, 2);
 
     const __half* ksc = reinterpret_cast<const __half*>(p.k_scale) + (int64_t)hk * p.ks_stride_h;
     const __half* vsc = reinterpret_cast<const __half*>(p.v_scale) + (int64_t)hk * p.vs_stride_h;
@@ -690,12 +659,9 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       // this warp's 32 tokens lie in half-tile q4/2 of the tile: the head's nth half-tile
       const int nth = 2 * t + (q4 >> 1);
       const int stage = g * kSlots + nth % kSlots, buf = t & 1;
-      if (q4 == 0) WSVD_TRACE(2 + g, t, 0);
       load_scales(slot_n, sk_n, sv_n);
       load_slot(s + 2 * kTile, slot_n);
-      if (q4 == 0) WSVD_TRACE(2 + g, t, 1);
       ok = wait_issued(stage, nth / kSlots + 1) && mbar_wait(bar_full(stage), (nth / kSlots) & 1);
-      if (q4 == 0) WSVD_TRACE(2 + g, t, 2);
       if (!ok) break;
 
       // ---- the warp's 32 K rows (lane = token) and V rows (lane (rg, tg): chunk rg of rows
@@ -723,7 +689,6 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       if (lane == 0) mbar_arrive(bar_empty(stage));
 
       ok = mbar_wait(bar_w_full(buf), (t >> 1) & 1);
-      if (q4 == 0) WSVD_TRACE(2 + g, t, 3);
       if (!ok) break;
       tc_fence_after();
 
@@ -755,7 +720,6 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_w_empty(buf));  // this warp has read its rows of W
-      if (q4 == 0) WSVD_TRACE(2 + g, t, 4);
       float d0, d1;
       upk(dot2, d0, d1);
       const float sk = __half2float(__ushort_as_half(sk_raw)), sv = __half2float(__ushort_as_half(sv_raw));
@@ -774,7 +738,6 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       const float pr = valid ? fast_exp2(z - m_w) : 0.f;
       l_lane += pr;
       const float pvs = pr * sv;
-      if (q4 == 0) WSVD_TRACE(2 + g, t, 5);
 
       // ---- P.V on the CUDA cores: this lane owns 16 ranks (chunk rg) of tokens tg + 8k
 #pragma unroll
@@ -791,7 +754,6 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
           acc[2 * jj + 1] = fma2(x23, pj2, acc[2 * jj + 1]);
         }
       }
-      if (q4 == 0) WSVD_TRACE(2 + g, t, 6);
       sk_raw = sk_n;
       sv_raw = sv_n;
     }
@@ -893,9 +855,6 @@ void encode_latent_maps(const WsvdLatentDecodeParams& p, TcArgs* ta) {
   ta->slot_axis = 1;
   memset(&ta->tmap_k, 0, sizeof(CUtensorMap));
   memset(&ta->tmap_v, 0, sizeof(CUtensorMap));
-#ifdef WSVD_TC_NO_TMA
-  return;
-#endif
   if (p.n_token_slots <= 0) return;
   int ax_k = 1;
   if (!encode_one(&ta->tmap_k, p.latent_k, p.k_stride_t, p.k_stride_h, p.n_token_slots, p.n_kv_heads, kRk,
@@ -937,12 +896,6 @@ cudaError_t launch_stage1_tc(const KArgs& a, const void* table, int table_rows, 
 cudaError_t read_tc_status(unsigned int* out) {
   return cudaMemcpyFromSymbol(out, tc::g_status, sizeof(unsigned int));
 }
-
-#ifdef WSVD_TC_TRACE
-extern "C" int wsvd_debug_read_trace(long long* dst) {
-  return (int)cudaMemcpyFromSymbol(dst, tc::g_trace, sizeof(long long) * 8 * 64 * 8);
-}
-#endif
 
 cudaError_t reset_tc_status() {
   const unsigned int zero = 0;

@@ -48,7 +48,9 @@ __global__ void __launch_bounds__(128) quant_append_kernel(const __grid_constant
     amax = fmaxf(amax, fabsf(v[i]));
   }
   amax = warp_max(amax);
-  const float scale = amax == 0.f ? 1.f : amax / 127.f;
+  // The stored scale is f16: amax/127 below the smallest positive f16 would round to 0 (and the
+  // divide below to inf/NaN), above the largest finite f16 to inf.  Clamp to the f16 range.
+  const float scale = amax == 0.f ? 1.f : fminf(fmaxf(amax / 127.f, 5.9604644775390625e-8f), 65504.f);
   const __half scale_h = __float2half_rn(scale);
   const float sf = __half2float(scale_h);
   int8_t* dst = reinterpret_cast<int8_t*>(is_v ? p.latent_v : p.latent_k) +

@@ -24,33 +24,38 @@ void* g_scratch_ptr[kMaxDevices] = {};  // device address of g_static_scratch, p
 
 // In host code `g_static_scratch` is only a handle; the address the kernels need comes from
 // cudaGetSymbolAddress, asked once per device with that device current.
-int scratch_for_current_device(void** out) {
+cudaError_t scratch_for_current_device(void** out) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return (int)e;
-  if (dev < 0 || dev >= kMaxDevices) return (int)cudaErrorInvalidDevice;
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
   std::lock_guard<std::mutex> lock(g_mutex);
   if (!g_scratch_ptr[dev]) {
     void* ptr = nullptr;
     e = cudaGetSymbolAddress(&ptr, g_static_scratch);
-    if (e != cudaSuccess) return (int)e;
+    if (e != cudaSuccess) return e;
     g_scratch_ptr[dev] = ptr;
   }
   *out = g_scratch_ptr[dev];
-  return 0;
+  return cudaSuccess;
 }
 
 }  // namespace
 
 extern "C" int wsvd_latent_decode_static(const WsvdLatentDecodeParams* p, void* stream) {
-  if (!p) return WSVD_ERR_NULL_POINTER;
+  // the same argument checks, in the same order, as the workspace entry point: an invalid
+  // block is reported as such whatever its batch size
+  const int st = wsvd::validate_decode_params(p);
+  if (st != WSVD_OK) return st;
   if (p->batch == 0) return WSVD_OK;
   const size_t need = wsvd_latent_decode_workspace_bytes(p);
-  if (need == 0) return WSVD_ERR_BAD_SHAPE;
   if (need > (size_t)WSVD_STATIC_SCRATCH_BYTES) return WSVD_ERR_TOO_LARGE;
   void* scratch = nullptr;
-  if (scratch_for_current_device(&scratch) != 0) return WSVD_ERR_CUDA;
+  const cudaError_t e = scratch_for_current_device(&scratch);
+  if (e != cudaSuccess) return wsvd::record_cuda_error(e);
   // Nothing in the scratch has to start at zero: every partial slot the merge reads is
   // written by stage 1 of the same call, and the position table is rebuilt when used.
+  // (The cached address stays valid for the life of the device's primary context; a host
+  // that calls cudaDeviceReset must not use this entry point afterwards.)
   return wsvd_latent_decode(p, scratch, (size_t)WSVD_STATIC_SCRATCH_BYTES, stream);
 }

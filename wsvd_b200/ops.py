@@ -38,16 +38,23 @@ def _cuda_tensor(name, t, dtypes, ndim, inner_contiguous=True):
 
 
 _TABLES = {}
+_RETIRED_TABLES = []  # superseded tables stay allocated: cached argument blocks and captured graphs may point at them
 _CALLS = {}
 
 
 def _sig(t):
-    return None if t is None else (t.data_ptr(), tuple(t.shape), tuple(t.stride()), t.dtype)
+    return None if t is None else (t.data_ptr(), t.shape, t.stride(), t.dtype)
 
 
-def rope_table(device, positions: int, head_dim: int = 128, theta: float = 10000.0):
+def rope_table(device, positions: int, head_dim: int = 128, theta: float = 10000.0, stream=None):
     """cos/sin position table for the tensor-core kernel, built once per
-    (device, theta, head_dim) and grown geometrically with the longest context seen."""
+    (device, theta, head_dim) and grown geometrically with the longest context seen.
+
+    Returns (buffer, rows, event).  The table is built on `stream` (default: the current
+    stream); `event` is recorded right after the build so that a launch on another stream
+    can order itself behind it.  A table that is replaced by a larger one is never freed:
+    argument blocks handed out earlier, and CUDA graphs captured with them, keep pointing
+    at memory that still holds a valid (shorter) table."""
     dev = torch.device(device)
     key = (dev.index if dev.index is not None else torch.cuda.current_device(), float(theta), int(head_dim))
     have = _TABLES.get(key)
@@ -59,10 +66,24 @@ def rope_table(device, positions: int, head_dim: int = 128, theta: float = 10000
     nbytes = int(_lib.lib().wsvd_rope_table_bytes(rows, head_dim))
     buf = torch.empty(nbytes, dtype=torch.uint8, device=dev)
     with torch.cuda.device(dev):
+        s = torch.cuda.current_stream() if stream is None else stream
         check(_lib.lib().wsvd_rope_table_init(_ptr(buf), nbytes, rows, head_dim, float(theta),
-                                              _stream(None)), "wsvd_rope_table_init")
-    _TABLES[key] = (buf, rows)
+                                              ctypes.c_void_p(s.cuda_stream)), "wsvd_rope_table_init")
+        ev = torch.cuda.Event()
+        ev.record(s)
+    if have is not None:
+        _RETIRED_TABLES.append(have)
+    _TABLES[key] = (buf, rows, ev, s.cuda_stream)
     return _TABLES[key]
+
+
+def _order_after_table(entry, stream) -> None:
+    """Make `stream` wait for the table's build when it was enqueued on another stream and
+    has not finished yet."""
+    _buf, _rows, ev, built_on = entry
+    s = torch.cuda.current_stream() if stream is None else stream
+    if s.cuda_stream != built_on and not ev.query():
+        s.wait_event(ev)
 
 
 def kernel_status() -> int:
@@ -75,7 +96,7 @@ def kernel_status() -> int:
 def build_params(
     q, b_seq_len, b_req_idx, req_to_token, max_len, latent_k, k_scale, latent_v, v_scale, wk, wk_scale=None,
     wv=None, out=None, pos_offset=None, theta=10000.0, sm_scale=0.0, rope_layout="half", split_len=0,
-    kernel="auto",
+    kernel="auto", stream=None,
 ) -> Tuple[LatentDecodeParams, list]:
     """Validate tensors and fill a WsvdLatentDecodeParams.  Returns the struct and the
     list of tensors it points into (keep them alive until the launch is enqueued)."""
@@ -153,7 +174,7 @@ def build_params(
     p.theta, p.sm_scale = float(theta), float(sm_scale)
     p.n_token_slots = min(latent_k.shape[0], latent_v.shape[0])
     if D == 128 and kernel != "generic":
-        table, rows = rope_table(q.device, int(max_len), D, theta)
+        table, rows = rope_table(q.device, int(max_len), D, theta, stream=stream)[:2]
         p.rope_table, p.rope_table_rows = table.data_ptr(), rows
     keep = [q, latent_k, latent_v, k_scale, v_scale, wk, wk_scale, wv, req_to_token, b_req_idx, b_seq_len,
             pos_offset, out]
@@ -175,6 +196,38 @@ def _stream(stream) -> ctypes.c_void_p:
     return ctypes.c_void_p(s.cuda_stream)
 
 
+def _cached_params(tag, q3, infer_state, latent_k, k_scale, latent_v, v_scale, wk, wk_scale, wv, pos_offset, theta,
+                   rope_layout, split_len, kernel, stream):
+    """A private copy of the validated argument block for this set of buffers and options.
+
+    A decode loop calls with the same buffers every step, so the validated block is kept
+    per (address, shape, stride) signature.  What can change underneath a cached block is
+    refreshed on every hit: the position table (it is replaced by a larger one when a
+    longer context arrives).  The caller gets a copy, so that filling in `out` does not
+    touch the cached block and calls from several threads do not share mutable state."""
+    rtt = infer_state.req_manager.req_to_token_indexs
+    max_len = int(infer_state.max_len_in_batch)
+    key = (tag, _sig(q3), _sig(infer_state.b_seq_len), _sig(infer_state.b_req_idx), _sig(rtt), max_len,
+           _sig(latent_k), _sig(k_scale), _sig(latent_v), _sig(v_scale), _sig(wk), _sig(wk_scale), _sig(wv),
+           _sig(pos_offset), float(theta), rope_layout, int(split_len), kernel)
+    hit = _CALLS.get(key)
+    if hit is None:
+        p, _keep = build_params(
+            q3, infer_state.b_seq_len, infer_state.b_req_idx, rtt, max_len, latent_k, k_scale, latent_v, v_scale,
+            wk, wk_scale, wv=wv, out=None, pos_offset=pos_offset, theta=theta, rope_layout=rope_layout,
+            split_len=split_len, kernel=kernel, stream=stream)
+        if len(_CALLS) >= 64:
+            _CALLS.clear()
+        hit = _CALLS[key] = (p, workspace_bytes(p))
+    cached, need = hit
+    p = LatentDecodeParams.from_buffer_copy(cached)
+    if cached.rope_table:
+        entry = rope_table(q3.device, max_len, p.head_dim, theta, stream=stream)
+        p.rope_table, p.rope_table_rows = entry[0].data_ptr(), entry[1]
+        _order_after_table(entry, stream)
+    return p, need
+
+
 @torch.no_grad()
 def latent_decode(
     q, infer_state, latent_k, k_scale, latent_v, v_scale, wk, wk_scale=None, *, wv=None, out=None,
@@ -186,23 +239,8 @@ def latent_decode(
     at least workspace_bytes(); when absent it is taken from `alloc_tensor_func`."""
     B = int(infer_state.batch_size)
     q3 = q.view(B, q.shape[-2], q.shape[-1]) if q.dim() != 3 else q
-    rtt = infer_state.req_manager.req_to_token_indexs
-    max_len = int(infer_state.max_len_in_batch)
-    # A decode loop calls with the same buffers every step: the validated argument block
-    # is kept per set of (address, shape, stride) and options.
-    key = (_sig(q3), _sig(infer_state.b_seq_len), _sig(infer_state.b_req_idx), _sig(rtt), max_len, _sig(latent_k),
-           _sig(k_scale), _sig(latent_v), _sig(v_scale), _sig(wk), _sig(wk_scale), _sig(wv), _sig(pos_offset),
-           float(theta), rope_layout, int(split_len), kernel)
-    hit = _CALLS.get(key)
-    if hit is None:
-        p, keep = build_params(
-            q3, infer_state.b_seq_len, infer_state.b_req_idx, rtt, max_len, latent_k, k_scale, latent_v, v_scale,
-            wk, wk_scale, wv=wv, out=None, pos_offset=pos_offset, theta=theta, rope_layout=rope_layout,
-            split_len=split_len, kernel=kernel)
-        if len(_CALLS) >= 64:
-            _CALLS.clear()
-        hit = _CALLS[key] = (p, workspace_bytes(p))
-    p, need = hit
+    p, need = _cached_params("decode", q3, infer_state, latent_k, k_scale, latent_v, v_scale, wk, wk_scale, wv,
+                             pos_offset, theta, rope_layout, split_len, kernel, stream)
     out_w = p.head_dim if wv is not None else p.rank_v
     if out is None:
         out = alloc_tensor_func((B, p.n_q_heads, out_w), dtype=q.dtype, device=q.device)
@@ -231,21 +269,8 @@ def latent_decode_gather(q, infer_state, latent_k, k_scale, latent_v, v_scale, w
     LOCAL heads."""
     B = int(infer_state.batch_size)
     q3 = q.view(B, q.shape[-2], q.shape[-1]) if q.dim() != 3 else q
-    rtt = infer_state.req_manager.req_to_token_indexs
-    max_len = int(infer_state.max_len_in_batch)
-    # same per-call-signature cache of the validated argument block as latent_decode
-    key = ("gather", _sig(q3), _sig(infer_state.b_seq_len), _sig(infer_state.b_req_idx), _sig(rtt), max_len,
-           _sig(latent_k), _sig(k_scale), _sig(latent_v), _sig(v_scale), _sig(wk), _sig(wk_scale), _sig(wv),
-           float(theta), rope_layout, int(split_len), kernel)
-    hit = _CALLS.get(key)
-    if hit is None:
-        p, _keep = build_params(q3, infer_state.b_seq_len, infer_state.b_req_idx, rtt, max_len, latent_k, k_scale,
-                                latent_v, v_scale, wk, wk_scale, wv=wv, out=None, theta=theta,
-                                rope_layout=rope_layout, split_len=split_len, kernel=kernel)
-        if len(_CALLS) >= 64:
-            _CALLS.clear()
-        hit = _CALLS[key] = (p, workspace_bytes(p))
-    p, need = hit
+    p, need = _cached_params("gather", q3, infer_state, latent_k, k_scale, latent_v, v_scale, wk, wk_scale, wv,
+                             None, theta, rope_layout, split_len, kernel, stream)
     if workspace is None:
         workspace = torch.empty(((need + 3) // 4,), dtype=torch.float32, device=q.device)
     have = workspace.numel() * workspace.element_size()
