@@ -73,16 +73,25 @@ def rope_table(device, positions: int, head_dim: int = 128, theta: float = 10000
         ev.record(s)
     if have is not None:
         _RETIRED_TABLES.append(have)
-    _TABLES[key] = (buf, rows, ev, s.cuda_stream)
+    _TABLES[key] = [buf, rows, ev, s.cuda_stream, False]
     return _TABLES[key]
 
 
 def _order_after_table(entry, stream) -> None:
     """Make `stream` wait for the table's build when it was enqueued on another stream and
-    has not finished yet."""
-    _buf, _rows, ev, built_on = entry
+    has not finished yet.  Once the build is known to have finished nothing is done (and no
+    event is queried, which a stream capture would not allow)."""
+    if entry[4]:
+        return
+    _buf, _rows, ev, built_on, _done = entry
     s = torch.cuda.current_stream() if stream is None else stream
-    if s.cuda_stream != built_on and not ev.query():
+    if torch.cuda.is_current_stream_capturing():
+        if s.cuda_stream != built_on:
+            s.wait_event(ev)  # becomes a dependency of the captured graph on the build
+        return
+    if ev.query():
+        entry[4] = True
+    elif s.cuda_stream != built_on:
         s.wait_event(ev)
 
 
