@@ -45,9 +45,11 @@ bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15)
 // runs on the generic kernel.
 bool tc_eligible(const WsvdLatentDecodeParams* p) {
   if (p->kernel == WSVD_KERNEL_GENERIC) return false;
-  if (p->head_dim != 128 || p->rank_k != 64) return false;
-  if (p->rank_v % 16 != 0 || p->rank_v > 64) return false;
-  if (p->latent_dtype != WSVD_I8 || p->pos_offset != nullptr) return false;
+  if (p->head_dim != 128) return false;
+  if (p->rank_k % 16 != 0 || p->rank_k > 64 || p->rank_v % 16 != 0 || p->rank_v > 64) return false;
+  if (p->latent_dtype != WSVD_I8) return false;
+  // with position offsets the table must reach max(pos_offset) + max_len, which only the caller knows
+  if (p->pos_offset != nullptr && p->rope_table == nullptr) return false;
   if (p->split_len % 128 != 0) return false;
   if (!aligned16(p->latent_k) || !aligned16(p->latent_v)) return false;
   if (p->k_stride_t % 16 || p->k_stride_h % 16 || p->v_stride_t % 16 || p->v_stride_h % 16) return false;

@@ -105,10 +105,14 @@ def kernel_status() -> int:
 def build_params(
     q, b_seq_len, b_req_idx, req_to_token, max_len, latent_k, k_scale, latent_v, v_scale, wk, wk_scale=None,
     wv=None, out=None, pos_offset=None, theta=10000.0, sm_scale=0.0, rope_layout="half", split_len=0,
-    kernel="auto", stream=None,
+    kernel="auto", stream=None, max_position=None,
 ) -> Tuple[LatentDecodeParams, list]:
     """Validate tensors and fill a WsvdLatentDecodeParams.  Returns the struct and the
-    list of tensors it points into (keep them alive until the launch is enqueued)."""
+    list of tensors it points into (keep them alive until the launch is enqueued).
+
+    `max_position`: with `pos_offset`, an upper bound of pos_offset[b] + len_b (the position
+    table must reach it); when absent it is read from `pos_offset` with a device
+    synchronisation."""
     _cuda_tensor("q", q, (torch.float16,), 3)
     B, Hq, D = q.shape
     _cuda_tensor("cache_latent_k", latent_k, (torch.int8, torch.float16), 3)
@@ -183,7 +187,10 @@ def build_params(
     p.theta, p.sm_scale = float(theta), float(sm_scale)
     p.n_token_slots = min(latent_k.shape[0], latent_v.shape[0])
     if D == 128 and kernel != "generic":
-        table, rows = rope_table(q.device, int(max_len), D, theta, stream=stream)[:2]
+        reach = int(max_len)
+        if pos_offset is not None:
+            reach = int(max_position) if max_position is not None else reach + max(0, int(pos_offset.max().item()))
+        table, rows = rope_table(q.device, reach, D, theta, stream=stream)[:2]
         p.rope_table, p.rope_table_rows = table.data_ptr(), rows
     keep = [q, latent_k, latent_v, k_scale, v_scale, wk, wk_scale, wv, req_to_token, b_req_idx, b_seq_len,
             pos_offset, out]
@@ -219,19 +226,24 @@ def _cached_params(tag, q3, infer_state, latent_k, k_scale, latent_v, v_scale, w
     key = (tag, _sig(q3), _sig(infer_state.b_seq_len), _sig(infer_state.b_req_idx), _sig(rtt), max_len,
            _sig(latent_k), _sig(k_scale), _sig(latent_v), _sig(v_scale), _sig(wk), _sig(wk_scale), _sig(wv),
            _sig(pos_offset), float(theta), rope_layout, int(split_len), kernel)
-    hit = _CALLS.get(key)
+    # position offsets may change inside the same buffer and decide how far the position table must
+    # reach, so such calls are validated (and the reach read back from the device) every time
+    hit = _CALLS.get(key) if pos_offset is None else None
     if hit is None:
         p, _keep = build_params(
             q3, infer_state.b_seq_len, infer_state.b_req_idx, rtt, max_len, latent_k, k_scale, latent_v, v_scale,
             wk, wk_scale, wv=wv, out=None, pos_offset=pos_offset, theta=theta, rope_layout=rope_layout,
             split_len=split_len, kernel=kernel, stream=stream)
-        if len(_CALLS) >= 64:
-            _CALLS.clear()
-        hit = _CALLS[key] = (p, workspace_bytes(p))
+        hit = (p, workspace_bytes(p))
+        if pos_offset is None:
+            if len(_CALLS) >= 64:
+                _CALLS.clear()
+            _CALLS[key] = hit
     cached, need = hit
     p = LatentDecodeParams.from_buffer_copy(cached)
     if cached.rope_table:
-        entry = rope_table(q3.device, max_len, p.head_dim, theta, stream=stream)
+        entry = rope_table(q3.device, max(max_len, cached.rope_table_rows if pos_offset is not None else 0),
+                           p.head_dim, theta, stream=stream)
         p.rope_table, p.rope_table_rows = entry[0].data_ptr(), entry[1]
         _order_after_table(entry, stream)
     return p, need
