@@ -377,6 +377,11 @@ class Measurement:
                                               case.v_scale, case.wk, None, wv=case.wv, out=self.out,
                                               split_len=args.split_len, kernel=args.kernel)
         self.split_len, self.n_splits = ops.plan(self.p)
+        # c1..c4 are shapes the tensor-core kernel accepts: without a split length from the caller the
+        # library then deals the batch's tiles out in equal shares, one persistent CTA per SM
+        self.balanced = args.split_len == 0 and args.kernel != "generic"
+        self.distribution = ("equal shares of 128-position tiles, one persistent CTA per SM" if self.balanced
+                             else "fixed-length splits, one CTA per (split, 4 heads, sequence)")
         self.ws = torch.empty((ops.workspace_bytes(self.p) + 3) // 4, dtype=torch.float32, device=dev)
         self.stream = torch.cuda.current_stream()
         self.lib = _lib.lib()
@@ -471,20 +476,15 @@ class Measurement:
         return self.timed(g.replay, steps) / steps
 
     def time_stage1(self, steps):
-        """The dominant kernel alone (stage 1), for the roofline."""
-        ct, case, spec = self.ct, self.case, self.spec
-        st = case.infer_state
-        n = self.B * self.H * self.n_splits * spec.rank_v
-        mid_o, lse = self.ws[:n], self.ws[n:]
-        p1, self._k1 = self.ops.build_params(case.q, st.b_seq_len, st.b_req_idx, st.req_manager.req_to_token_indexs,
-                                             st.max_len_in_batch, case.latent_k, case.k_scale, case.latent_v,
-                                             case.v_scale, case.wk, None, split_len=self.split_len,
-                                             kernel=self.args.kernel)
+        """The dominant kernel alone, for the roofline: the op without its merge kernel, with the
+        same work distribution as the whole op (the launch of the small kernel that cuts the
+        work into per-SM shares, where the op uses one, is inside the timed region)."""
+        ct = self.ct
 
         def stage1():
-            self._lib.check(self.lib.wsvd_latent_decode_stage1(
-                ct.byref(p1), ct.c_void_p(mid_o.data_ptr()), ct.c_void_p(lse.data_ptr()), self.n_splits,
-                ct.c_void_p(self.stream.cuda_stream)), "stage1")
+            self._lib.check(self.lib.wsvd_latent_decode_partials(
+                ct.byref(self.p), ct.c_void_p(self.ws.data_ptr()), self.ws.numel() * 4,
+                ct.c_void_p(self.stream.cuda_stream)), "wsvd_latent_decode_partials")
 
         for _ in range(3):
             stage1()
@@ -641,7 +641,8 @@ def main():
             "vs_baseline": None,
             "dtype": "i8 latents, f16 tensor-core operands, f32 accumulate/softmax", "data": "synthetic",
             "config": workload_config(spec, m.H, world),
-            "plan": {"split_len": m.split_len, "n_splits": m.n_splits, "kernel": args.kernel,
+            "plan": {"distribution": m.distribution, "split_len": m.split_len if not m.balanced else None,
+                     "n_splits": m.n_splits if not m.balanced else None, "kernel": args.kernel,
                      "collective": m.collective},
             "roofline": {
                 "bound": "hbm", "kernel": "latent decode stage 1", "achieved": achieved, "peak": peak,
@@ -654,7 +655,8 @@ def main():
             "gather_check": gather_ok,
             "e2e": {"value": m.bytes_total / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "us_per_layer": ms_e2e * 1e3,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": args.steps * 2,
+            # per step: [the kernel that cuts the tiles into per-SM shares,] stage 1, merge (+ gather)
+            "gpu_launches": args.steps * (3 if m.balanced else 2),
             "kernel_status": int(status.item()),
             "clocks": clocks,
         }

@@ -103,6 +103,38 @@ def test_c4_shortest_longest_and_one_more_40_heads_rank_64_48(kernel):
     _run_both_outputs(case, kernel, spec.max_len, _full_batch_split_len(spec, c, kernel), "c4")
 
 
+# ---- equal shares of tiles over persistent CTAs (what the op does when no split length is given) ----
+
+@pytest.mark.parametrize("heads,lens", [
+    (6, [1500, 0, 257, 0, 2049]),              # a last group of 2 heads; sequences without tokens
+    (8, [0, 0, 129, 128, 1, 0, 4000, 127]),    # leading/trailing empty sequences, one-token sequence
+    (40, [3000, 17]),                          # more tiles than CTAs: several items per share
+    (4, [128] * 200),                          # more sequences than CTAs: many one-tile items per share
+], ids=["h6-zero-lengths", "h8-edges", "h40-long", "b200-one-tile"])
+def test_balanced_shares_on_ragged_batches(heads, lens):
+    case = inputs.make_case(len(lens), heads, 128, 64, 48, lens, max(lens), seed=61)
+    c = case.to("cuda")
+    want_lat, want = oracle_for(case), oracle_for(case, wv=True)
+    for _ in range(2):  # the second call reuses the workspace the first one left behind
+        got_lat = op_i8(c.q, c.infer_state, heads, 128, c.latent_k, c.k_scale, c.latent_v, c.v_scale, c.wk, None,
+                        kernel="tc")
+        got = op_i8(c.q, c.infer_state, heads, 128, c.latent_k, c.k_scale, c.latent_v, c.v_scale, c.wk, None, wv=c.wv,
+                    kernel="tc")
+        torch.cuda.synchronize()
+        assert ops.kernel_status() == 0, "a bounded wait timed out"
+        assert_close(got_lat, want_lat, "balanced O_lat")
+        assert_close(got, want, "balanced O")
+
+
+def test_all_sequences_empty():
+    case = inputs.make_case(3, 4, 128, 64, 64, [0, 0, 0], 1, seed=62)
+    c = case.to("cuda")
+    got = op_i8(c.q, c.infer_state, 4, 128, c.latent_k, c.k_scale, c.latent_v, c.v_scale, c.wk, None, kernel="tc")
+    torch.cuda.synchronize()
+    assert ops.kernel_status() == 0
+    assert torch.count_nonzero(got).item() == 0
+
+
 # ---- the raw C entry points on paths the Python op never takes ----
 
 def _raw_params(c, out, **kw):

@@ -52,6 +52,7 @@ bool tc_eligible(const WsvdLatentDecodeParams* p) {
   if (p->pos_offset != nullptr && p->rope_table == nullptr) return false;
   if (p->split_len % 128 != 0) return false;
   if (!aligned16(p->latent_k) || !aligned16(p->latent_v)) return false;
+  if (!aligned16(p->q) || p->q_stride_b % 8 || p->q_stride_h % 8) return false;  // 16-byte loads of q
   if (p->k_stride_t % 16 || p->k_stride_h % 16 || p->v_stride_t % 16 || p->v_stride_h % 16) return false;
   if (p->rope_table && (!aligned16(p->rope_table) || p->rope_table_rows < ((p->max_len + 127) / 128) * 128))
     return false;
@@ -107,8 +108,10 @@ void fill_args(const WsvdLatentDecodeParams* p, float* mid_o, float* lse, int sp
   a->sm_scale = p->sm_scale != 0.f ? p->sm_scale : (float)(1.0 / sqrt((double)p->head_dim));
 }
 
-// `scratch_table`: where to build the position table when the caller gave none (may be null).
-int run_stage1(const wsvd::KArgs& a, void* scratch_table, cudaStream_t stream) {
+// `scratch_table`: where to build the position table when the caller gave none (may be null);
+// `cta_plan`: the balanced work plan for n_ctas persistent CTAs of the tensor-core kernel, or null
+// (fixed-length splits, partials in the [B, Hq, n_splits] layout).
+int run_stage1(const wsvd::KArgs& a, void* scratch_table, const void* cta_plan, int n_ctas, cudaStream_t stream) {
   if (a.p.batch == 0) return WSVD_OK;
   const bool tc = tc_eligible(&a.p) && a.split_len % 128 == 0 && (a.p.rope_table || scratch_table);
   if (!tc) {
@@ -124,14 +127,62 @@ int run_stage1(const wsvd::KArgs& a, void* scratch_table, cudaStream_t stream) {
     if (e != cudaSuccess) return cuda_fail(e);
     table = scratch_table;
   }
-  cudaError_t e = wsvd::launch_stage1_tc(a, table, rows, stream);
+  cudaError_t e = wsvd::launch_stage1_tc(a, table, rows, cta_plan, n_ctas, stream);
   return e == cudaSuccess ? WSVD_OK : cuda_fail(e);
 }
 
-size_t partial_bytes(const WsvdLatentDecodeParams* p, int ns) {
-  const size_t slots = (size_t)p->batch * p->n_q_heads * ns;
-  const size_t b = slots * ((size_t)p->rank_v + 1) * sizeof(float);
-  return (b + 255) & ~(size_t)255;
+// Without a split length from the caller, a problem the tensor-core kernel can run is cut into
+// equal shares of tiles, one per SM, instead of fixed-length splits.
+bool balanced_mode(const WsvdLatentDecodeParams* p) { return p->split_len == 0 && tc_eligible(p); }
+
+size_t align256(size_t b) { return (b + 255) & ~(size_t)255; }
+
+// Workspace: partials (mid_o, then lse), [balanced mode: tile prefix sums per sequence, per-CTA
+// plan,] [the position table when the caller passed none].  Sizes do not depend on the device.
+struct Layout {
+  size_t slots;       // partial results: one per (sequence, head, split) or per (item, head of the group)
+  size_t prefix_off;  // balanced mode only
+  size_t plan_off;
+  size_t table_off;
+  size_t total;
+};
+Layout workspace_layout(const WsvdLatentDecodeParams* p, int n_splits) {
+  Layout l = {};
+  const bool bal = balanced_mode(p);
+  const size_t n_hg = ((size_t)p->n_q_heads + wsvd::kBalancedGroup - 1) / wsvd::kBalancedGroup;
+  l.slots = bal ? ((size_t)p->batch * n_hg + wsvd::kMaxBalancedCtas) * wsvd::kBalancedGroup
+                : (size_t)p->batch * p->n_q_heads * n_splits;
+  size_t off = align256(l.slots * ((size_t)p->rank_v + 1) * sizeof(float));
+  if (bal) {
+    l.prefix_off = off;
+    off += align256(((size_t)p->batch + 2) * sizeof(int32_t));
+    l.plan_off = off;
+    off += (size_t)wsvd::kMaxBalancedCtas * 16;
+  }
+  l.table_off = off;
+  if (tc_eligible(p) && !p->rope_table) off += wsvd::rope_table_bytes(table_rows_for(p->max_len));
+  l.total = off;
+  return l;
+}
+
+// persistent CTAs of the balanced mode: one per SM, never more than there can be tiles
+int balanced_ctas(const WsvdLatentDecodeParams* p, int* n_ctas) {
+  static int sm_count[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e);
+  int sms = dev >= 0 && dev < 64 ? sm_count[dev] : 0;
+  if (sms == 0) {
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (dev >= 0 && dev < 64) sm_count[dev] = sms;
+  }
+  const long n_hg = (p->n_q_heads + wsvd::kBalancedGroup - 1) / wsvd::kBalancedGroup;
+  const long most = (long)p->batch * n_hg * ((p->max_len + 127) / 128);
+  long n = sms < wsvd::kMaxBalancedCtas ? sms : wsvd::kMaxBalancedCtas;
+  if (n > most) n = most;
+  *n_ctas = n < 1 ? 1 : (int)n;
+  return WSVD_OK;
 }
 
 }  // namespace
@@ -177,9 +228,7 @@ size_t wsvd_latent_decode_workspace_bytes(const WsvdLatentDecodeParams* p) {
   if (!p || p->max_len < 0 || p->split_len < 0 || p->batch < 0 || p->n_q_heads <= 0 || p->rank_v <= 0) return 0;
   int sl, ns;
   plan(p, &sl, &ns);
-  size_t bytes = partial_bytes(p, ns);
-  if (tc_eligible(p) && !p->rope_table) bytes += wsvd::rope_table_bytes(table_rows_for(p->max_len));
-  return bytes;
+  return workspace_layout(p, ns).total;
 }
 
 size_t wsvd_rope_table_bytes(int32_t positions, int32_t head_dim) {
@@ -237,8 +286,8 @@ int wsvd_latent_quant_append_i8(const WsvdQuantAppendParams* p, void* stream) {
 }
 
 static int decode_impl(const WsvdLatentDecodeParams* p, const WsvdPeerSet* peers, void* workspace,
-                       size_t workspace_bytes, void* stream) {
-  int st = validate(p, peers == nullptr);
+                       size_t workspace_bytes, void* stream, bool merge = true) {
+  int st = validate(p, peers == nullptr && merge);
   if (st != WSVD_OK) return st;
   if (p->batch == 0) return WSVD_OK;
   const size_t need = wsvd_latent_decode_workspace_bytes(p);
@@ -247,26 +296,44 @@ static int decode_impl(const WsvdLatentDecodeParams* p, const WsvdPeerSet* peers
   if ((reinterpret_cast<uintptr_t>(workspace) & 15) != 0) return WSVD_ERR_BAD_STRIDE;
   int sl, ns;
   plan(p, &sl, &ns);
-  const size_t slots = (size_t)p->batch * p->n_q_heads * ns;
-  float* mid_o = reinterpret_cast<float*>(workspace);
-  float* lse = mid_o + slots * p->rank_v;
+  const Layout l = workspace_layout(p, ns);
+  uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+  float* mid_o = reinterpret_cast<float*>(ws);
+  float* lse = mid_o + l.slots * p->rank_v;
   wsvd::KArgs a;
   fill_args(p, mid_o, lse, sl, ns, &a);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  void* scratch_table = p->rope_table ? nullptr : reinterpret_cast<uint8_t*>(workspace) + partial_bytes(p, ns);
-  st = run_stage1(a, scratch_table, s);
-  if (st != WSVD_OK) return st;
+  void* scratch_table = p->rope_table ? nullptr : ws + l.table_off;
+  wsvd::PartialIndex where = {nullptr, 0, ns, sl};
+  const void* cta_plan = nullptr;
+  if (balanced_mode(p)) {
+    st = balanced_ctas(p, &where.n_ctas);
+    if (st != WSVD_OK) return st;
+    where.prefix = reinterpret_cast<const int32_t*>(ws + l.prefix_off);
+    cta_plan = ws + l.plan_off;
+    const cudaError_t e = wsvd::launch_balance_plan(
+        p->b_seq_len, p->batch, (p->n_q_heads + wsvd::kBalancedGroup - 1) / wsvd::kBalancedGroup, where.n_ctas,
+        reinterpret_cast<int32_t*>(ws + l.prefix_off), ws + l.plan_off, s);
+    if (e != cudaSuccess) return cuda_fail(e);
+  }
+  st = run_stage1(a, scratch_table, cta_plan, where.n_ctas, s);
+  if (st != WSVD_OK || !merge) return st;
   cudaError_t e =
-      peers ? wsvd::launch_stage2_peers(mid_o, lse, p->b_seq_len, *peers, p->batch, p->n_q_heads, ns, p->rank_v, sl,
+      peers ? wsvd::launch_stage2_peers(mid_o, lse, p->b_seq_len, *peers, p->batch, p->n_q_heads, where, p->rank_v,
                                         p->wv, p->wv_stride_r, p->n_kv_heads, p->head_dim, s)
             : wsvd::launch_stage2(mid_o, lse, p->b_seq_len, p->out, p->out_stride_b, p->out_stride_h, p->batch,
-                                  p->n_q_heads, ns, p->rank_v, sl, p->wv, p->wv_stride_r, p->n_kv_heads,
+                                  p->n_q_heads, where, p->rank_v, p->wv, p->wv_stride_r, p->n_kv_heads,
                                   p->head_dim, s);
   return e == cudaSuccess ? WSVD_OK : cuda_fail(e);
 }
 
 int wsvd_latent_decode(const WsvdLatentDecodeParams* p, void* workspace, size_t workspace_bytes, void* stream) {
   return decode_impl(p, nullptr, workspace, workspace_bytes, stream);
+}
+
+int wsvd_latent_decode_partials(const WsvdLatentDecodeParams* p, void* workspace, size_t workspace_bytes,
+                                void* stream) {
+  return decode_impl(p, nullptr, workspace, workspace_bytes, stream, false);
 }
 
 int wsvd_latent_decode_gather(const WsvdLatentDecodeParams* p, const WsvdPeerSet* peers, void* workspace,
@@ -323,7 +390,7 @@ int wsvd_latent_decode_stage1(const WsvdLatentDecodeParams* p, float* mid_o, flo
   if ((long)n_splits * p->split_len < p->max_len) return WSVD_ERR_WORKSPACE_TOO_SMALL;
   wsvd::KArgs a;
   fill_args(p, mid_o, lse, p->split_len, n_splits, &a);
-  return run_stage1(a, nullptr, reinterpret_cast<cudaStream_t>(stream));
+  return run_stage1(a, nullptr, nullptr, 0, reinterpret_cast<cudaStream_t>(stream));
 }
 
 static void dense_plan(const WsvdDenseDecodeParams* p, int* sl, int* ns) {
@@ -382,7 +449,8 @@ int wsvd_dense_decode_f16(const WsvdDenseDecodeParams* p, void* workspace, size_
   cudaError_t e = wsvd::launch_dense_stage1(a, s);
   if (e != cudaSuccess) return cuda_fail(e);
   e = wsvd::launch_stage2(a.mid_o, a.lse, p->b_seq_len, p->out, p->out_stride_b, p->out_stride_h, p->batch,
-                          p->n_q_heads, ns, p->head_dim, sl, nullptr, 0, 1, p->head_dim, s);
+                          p->n_q_heads, wsvd::PartialIndex{nullptr, 0, ns, sl}, p->head_dim, nullptr, 0, 1,
+                          p->head_dim, s);
   return e == cudaSuccess ? WSVD_OK : cuda_fail(e);
 }
 
@@ -398,8 +466,8 @@ int wsvd_decode_stage2(const float* mid_o, const float* lse, const int32_t* b_se
     return WSVD_ERR_BAD_SHAPE;
   if (batch == 0) return WSVD_OK;
   cudaError_t e = wsvd::launch_stage2(mid_o, lse, b_seq_len, out, out_stride_b, out_stride_h, batch, n_q_heads,
-                                      n_splits, width, split_len, wv, wv_stride_r, wv ? n_kv_heads : 1, head_dim,
-                                      reinterpret_cast<cudaStream_t>(stream));
+                                      wsvd::PartialIndex{nullptr, 0, n_splits, split_len}, width, wv, wv_stride_r,
+                                      wv ? n_kv_heads : 1, head_dim, reinterpret_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? WSVD_OK : cuda_fail(e);
 }
 

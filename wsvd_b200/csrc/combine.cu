@@ -41,25 +41,40 @@ __device__ __forceinline__ uint64_t global_ns() {
 template <bool kPeers>
 __global__ void __launch_bounds__(kThreads)
 stage2_kernel(const float* __restrict__ mid_o, const float* __restrict__ lse, const int32_t* __restrict__ b_seq_len,
-              __half* __restrict__ out, int64_t out_stride_b, int64_t out_stride_h, int n_q_heads, int n_splits,
-              int width, int split_len, const __half* __restrict__ wv, int64_t wv_stride_r, int n_kv_heads,
+              __half* __restrict__ out, int64_t out_stride_b, int64_t out_stride_h, int n_q_heads,
+              const PartialIndex where, int width, const __half* __restrict__ wv, int64_t wv_stride_r, int n_kv_heads,
               int head_dim, const __grid_constant__ PeerArgs pa) {
   const int h = blockIdx.x, b = blockIdx.y;
   const int n = b_seq_len[b];
-  const int ns = n <= 0 ? 0 : min(n_splits, (n + split_len - 1) / split_len);
-  const int64_t slot0 = ((int64_t)b * n_q_heads + h) * n_splits;
+  // partial i of this (sequence, head) sits in slot slot0 + i * step
+  int ns = 0;
+  int64_t slot0 = 0, step = 1;
+  if (n > 0 && where.prefix == nullptr) {
+    ns = min(where.n_splits, (n + where.split_len - 1) / where.split_len);
+    slot0 = ((int64_t)b * n_q_heads + h) * where.n_splits;
+  } else if (n > 0) {
+    const int n_hg = (n_q_heads + kBalancedGroup - 1) / kBalancedGroup, hg = h / kBalancedGroup;
+    const int before = where.prefix[b], tiles_b = where.prefix[b + 1] - before;
+    const int64_t total = (int64_t)where.prefix[gridDim.y] * n_hg;
+    const int shares = where.prefix[gridDim.y + 1];
+    const int64_t first = (int64_t)before * n_hg + (int64_t)hg * tiles_b;
+    const int c0 = share_owner(first, total, shares), c1 = share_owner(first + tiles_b - 1, total, shares);
+    ns = c1 - c0 + 1;
+    slot0 = ((int64_t)b * n_hg + hg + c0) * kBalancedGroup + h % kBalancedGroup;
+    step = kBalancedGroup;
+  }
   __shared__ float row[128];
 
   // every thread computes the (tiny) max and weight sum itself: ns <= a few hundred
   float m = -INFINITY;
-  for (int i = 0; i < ns; ++i) m = fmaxf(m, lse[slot0 + i]);
+  for (int i = 0; i < ns; ++i) m = fmaxf(m, lse[slot0 + i * step]);
   float wsum = 0.f;
-  for (int i = 0; i < ns; ++i) wsum += __expf(lse[slot0 + i] - m);
+  for (int i = 0; i < ns; ++i) wsum += __expf(lse[slot0 + i * step] - m);
 
   const int r = threadIdx.x;
   float o = 0.f;
   if (r < width && ns > 0) {
-    for (int i = 0; i < ns; ++i) o = fmaf(__expf(lse[slot0 + i] - m), mid_o[(slot0 + i) * width + r], o);
+    for (int i = 0; i < ns; ++i) o = fmaf(__expf(lse[slot0 + i * step] - m), mid_o[(slot0 + i * step) * width + r], o);
     o /= wsum;
   }
   const int64_t doff = (int64_t)b * out_stride_b + (int64_t)(h + (kPeers ? pa.head_offset : 0)) * out_stride_h;
@@ -157,20 +172,20 @@ stage2_kernel(const float* __restrict__ mid_o, const float* __restrict__ lse, co
 }  // namespace
 
 cudaError_t launch_stage2(const float* mid_o, const float* lse, const int32_t* b_seq_len, void* out,
-                          int64_t out_stride_b, int64_t out_stride_h, int batch, int n_q_heads, int n_splits,
-                          int width, int split_len, const void* wv, int64_t wv_stride_r, int n_kv_heads,
+                          int64_t out_stride_b, int64_t out_stride_h, int batch, int n_q_heads,
+                          const PartialIndex& where, int width, const void* wv, int64_t wv_stride_r, int n_kv_heads,
                           int head_dim, cudaStream_t stream) {
   dim3 grid(n_q_heads, batch);
   stage2_kernel<false><<<grid, kThreads, 0, stream>>>(mid_o, lse, b_seq_len, reinterpret_cast<__half*>(out),
-                                                      out_stride_b, out_stride_h, n_q_heads, n_splits, width,
-                                                      split_len, reinterpret_cast<const __half*>(wv), wv_stride_r,
+                                                      out_stride_b, out_stride_h, n_q_heads, where, width,
+                                                      reinterpret_cast<const __half*>(wv), wv_stride_r,
                                                       n_kv_heads, head_dim, PeerArgs{});
   return cudaGetLastError();
 }
 
 cudaError_t launch_stage2_peers(const float* mid_o, const float* lse, const int32_t* b_seq_len,
-                                const WsvdPeerSet& peers, int batch, int n_q_heads, int n_splits, int width,
-                                int split_len, const void* wv, int64_t wv_stride_r, int n_kv_heads, int head_dim,
+                                const WsvdPeerSet& peers, int batch, int n_q_heads, const PartialIndex& where,
+                                int width, const void* wv, int64_t wv_stride_r, int n_kv_heads, int head_dim,
                                 cudaStream_t stream) {
   PeerArgs pa{};
   for (int i = 0; i < peers.n_peers; ++i) {
@@ -186,7 +201,7 @@ cudaError_t launch_stage2_peers(const float* mid_o, const float* lse, const int3
   pa.timeout_ns = peers.timeout_ms > 0 ? (uint64_t)peers.timeout_ms * 1000000ull : 2000000000ull;
   dim3 grid(n_q_heads, batch);
   stage2_kernel<true><<<grid, kThreads, 0, stream>>>(mid_o, lse, b_seq_len, nullptr, peers.out_stride_b,
-                                                     peers.out_stride_h, n_q_heads, n_splits, width, split_len,
+                                                     peers.out_stride_h, n_q_heads, where, width,
                                                      reinterpret_cast<const __half*>(wv), wv_stride_r, n_kv_heads,
                                                      head_dim, pa);
   return cudaGetLastError();

@@ -50,6 +50,29 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// Balanced work distribution of the tensor-core kernel: `total` tiles in a fixed order are cut into
+// n_ctas shares; share c is [share_begin(c), share_begin(c + 1)), and share_owner inverts that.
+__host__ __device__ __forceinline__ int64_t share_begin(int c, int64_t total, int n_ctas) {
+  return (int64_t)c * total / n_ctas;
+}
+// the c with share_begin(c) <= tile < share_begin(c + 1), for 0 <= tile < total
+__host__ __device__ __forceinline__ int share_owner(int64_t tile, int64_t total, int n_ctas) {
+  return (int)(((tile + 1) * n_ctas - 1) / total);
+}
+constexpr int kBalancedGroup = 4;  // query heads per work item of the tensor-core kernel
+constexpr int kMaxBalancedCtas = 256;
+
+// Where the merge finds the partials.  Split mode (prefix null): [B, Hq, n_splits] slots, the first
+// ceil(len / split_len) of a row used.  Balanced mode: slot (b * n_hg + hg + c) * 4 + h % 4 for every
+// CTA c whose share holds tiles of (sequence b, head group hg); prefix[b] = tiles in sequences before
+// b, prefix[batch + 1] = number of shares (both written by the plan kernel).
+struct PartialIndex {
+  const int32_t* prefix;  // [batch + 2], or null
+  int32_t n_ctas;         // CTAs of the stage-1 grid (>= the number of shares)
+  int32_t n_splits;
+  int32_t split_len;
+};
+
 // Shared by the entry points that live outside capi.cu: the argument checks of
 // wsvd_latent_decode, and the per-thread record behind wsvd_last_cuda_error()
 // (returns WSVD_ERR_CUDA).
@@ -58,15 +81,21 @@ int record_cuda_error(cudaError_t e);
 
 // Launchers implemented in the kernel translation units.
 cudaError_t launch_stage1_generic(const KArgs& a, cudaStream_t stream);
-cudaError_t launch_stage1_tc(const KArgs& a, const void* table, int table_rows, cudaStream_t stream);
+// `cta_plan`: the output of launch_balance_plan for a grid of n_ctas persistent CTAs (partials in the
+// balanced layout), or null: one CTA per (split, head group, sequence), partials in the split layout.
+cudaError_t launch_stage1_tc(const KArgs& a, const void* table, int table_rows, const void* cta_plan, int n_ctas,
+                             cudaStream_t stream);
+// prefix: [batch + 2] int32; cta_plan: n_ctas x 16 bytes (16-byte aligned)
+cudaError_t launch_balance_plan(const int32_t* b_seq_len, int batch, int n_hg, int n_ctas, int32_t* prefix,
+                                void* cta_plan, cudaStream_t stream);
 cudaError_t launch_rope_table(void* table, int rows, const KArgs& a, cudaStream_t stream);
 size_t rope_table_bytes(int rows);
 cudaError_t read_tc_status(unsigned int* out);
 cudaError_t reset_tc_status();
 cudaError_t launch_dense_stage1(const DenseArgs& a, cudaStream_t stream);
 cudaError_t launch_stage2_peers(const float* mid_o, const float* lse, const int32_t* b_seq_len,
-                                const WsvdPeerSet& peers, int batch, int n_q_heads, int n_splits, int width,
-                                int split_len, const void* wv, int64_t wv_stride_r, int n_kv_heads, int head_dim,
+                                const WsvdPeerSet& peers, int batch, int n_q_heads, const PartialIndex& where,
+                                int width, const void* wv, int64_t wv_stride_r, int n_kv_heads, int head_dim,
                                 cudaStream_t stream);
 cudaError_t read_peer_status(unsigned int* out);
 cudaError_t reset_peer_status();
@@ -74,8 +103,8 @@ cudaError_t launch_quant_append(const WsvdQuantAppendParams& p, cudaStream_t str
 cudaError_t read_append_status(unsigned int* out);
 cudaError_t reset_append_status();
 cudaError_t launch_stage2(const float* mid_o, const float* lse, const int32_t* b_seq_len, void* out,
-                          int64_t out_stride_b, int64_t out_stride_h, int batch, int n_q_heads, int n_splits,
-                          int width, int split_len, const void* wv, int64_t wv_stride_r, int n_kv_heads,
+                          int64_t out_stride_b, int64_t out_stride_h, int batch, int n_q_heads,
+                          const PartialIndex& where, int width, const void* wv, int64_t wv_stride_r, int n_kv_heads,
                           int head_dim, cudaStream_t stream);
 
 }  // namespace wsvd

@@ -15,7 +15,8 @@
 // operand [P;Q] is built once per CTA and stays in shared memory, the accumulator is fp32
 // in tensor memory (three 128-column buffers).  Each epilogue thread owns one token: it
 // reads its row of W from tensor memory and dots it in fp32 with the token's int8 K row,
-// which it fetched itself from global memory into registers one tile ahead.
+// which it copied from the K ring into registers at the top of the tile (so that the ring
+// slot is refilled a whole tile before its next use).
 //
 // Values.  O[r] = sum_s p_s sv_s Lv[s,r] is a true contraction over the tokens and runs on
 // the tensor cores as an int8 MMA (kind::i8): the A operand is the V half-tile exactly as
@@ -27,14 +28,31 @@
 // that fp32 would keep: 24 bits relative to the largest weight of the tile.  The softmax
 // denominator is accumulated by the owner threads in fp32.
 //
-// CTA = one (split, group of 4 heads, sequence); 20 warps:
+// Work.  A work item is a run of consecutive tiles of one (sequence, group of 4 heads); it ends
+// in one partial result (normalised latent-space row + log-sum-exp per head) for the merge kernel.
+//  - Balanced mode (cta_plan given): all tiles of the batch, ordered by (sequence, head group,
+//    tile), are cut into gridDim.x equal shares, one per persistent CTA (one CTA per SM).  A share
+//    covers a few items: the tail of one (sequence, head group), whole ones, the head of another.
+//    No SM idles in a partial last wave whatever the sequence lengths, the [P;Q] build is paid
+//    once per item, and tensor memory is allocated once.  balance_plan_kernel computes the shares
+//    from the sequence lengths on the device; the partial of item (sequence b, head group hg) of
+//    CTA c goes to slot (b * n_hg + hg + c), which is unique because along the tile order every
+//    new item advances the (sequence, head group) index or the CTA index.
+//  - Split mode (no plan): CTA blockIdx.x handles split blockIdx.x % n_splits of a fixed-length
+//    split plan, partials in the [B, Hq, n_splits] layout of the reference's stage 1.
+// 20 warps:
 //   warps 0-15   epilogue, 4 per head: warp w owns tensor-memory lanes 32*(w%4)..+31, i.e.
 //                tokens 32*(w%4).. of every tile of head w/4; lane 0 of the head's first warp
 //                issues the head's value MMAs
-//   warp 16      one thread issues the table-tile loads and the score MMAs
-//   warps 17-19  request the V rows: every head has a ring of kVSlots half-tiles; one TMA
-//                tensor copy per half-tile when its token slots are consecutive (lane g serves
-//                head g), else a gather of rows with 16-byte cp.async through the page table
+//   warp 16      one thread issues the score MMAs
+//   warp 17      requests the table tiles and the K rows
+//   warps 18-19  one pair of heads each: request the V rows, issue the pair's value MMAs
+// Latent rows travel in units of half a tile (64 tokens) of ALL the group's heads: one TMA tensor
+// copy of 16 KB (64 bytes x 64 token slots x 4 heads) when the unit's token slots are consecutive
+// and the cache is head-major, else one copy per head, else a gather of rows with 16-byte
+// cp.async through the page table.  A thread needs several hundred cycles to wait for a slot and
+// issue one copy, whatever its size, so the copies are few and large: 5 per tile and CTA (one
+// table tile, two K units, two V units), spread over three warps.
 // Every wait inside the tile loop is an mbarrier wait with a time limit; on a time-out the
 // kernel records a status code and every role falls through to the common exit, which frees
 // the tensor memory.
@@ -47,6 +65,7 @@ namespace wsvd {
 namespace tc {
 
 constexpr int kG = 4;          // heads per CTA
+static_assert(kG == kBalancedGroup, "the merge kernel indexes balanced partials by groups of kG heads");
 constexpr int kTile = 128;     // positions per MMA tile (= tensor-memory lanes)
 constexpr int kHalf = kTile / 2;
 constexpr int kRkMax = 64;
@@ -54,41 +73,44 @@ constexpr int kEpiWarps = 4 * kG;
 constexpr int kMmaWarp = kEpiWarps;
 constexpr int kProducers = 3;  // with the MMA warp they fill one warp slot per scheduler
 constexpr int kThreads = (kEpiWarps + 1 + kProducers) * 32;
-constexpr int kVSlots = 5;     // half-tiles of V in flight or in use, per head
+constexpr int kKSlots = 2;     // half-tiles of K per head: copied to registers at the top of their tile
+constexpr int kVSlots = 4;     // half-tiles of V: the tile whose value MMAs are pending, and the next tile in flight
 constexpr int kWBufs = 3;      // W accumulators of 128 columns (one pair of heads each)
 
-constexpr uint32_t kVSlotBytes = kHalf * 64;        // 64 tokens x 64 bytes (rank_v < 64: zero-filled)
+constexpr uint32_t kHeadBytes = kHalf * 64;         // one head's part of a unit: 64 tokens x 64 bytes (rank < 64: zero-filled)
+constexpr uint32_t kUnitBytes = kG * kHeadBytes;    // a ring slot: half a tile of K or V for up to 4 KV heads
 constexpr uint32_t kAHalfBytes = kTile * 128;       // 128 rows x 64 f16
 constexpr uint32_t kABufBytes = 2 * kAHalfBytes;    // cos half + sin half
 constexpr uint32_t kBHalfBytes = kG * kRkMax * 128; // 256 rows x 64 f16
-constexpr uint32_t kPlaneBytes = 256;               // per warp: 2 chunks of 16 tokens x 8 rows x 16 bytes
+constexpr uint32_t kPlaneBytes = 256;               // per pair of warps: 2 chunks of 16 tokens x 8 rows x 16 bytes
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kTmemD = kWBufs * 128;           // first column of the value accumulators (8 per head)
+constexpr uint32_t kTmemD = kWBufs * 128;           // first column of the value accumulators: 8 per (head, warp)
 constexpr float kPlaneScale = 16776960.f;           // 2^24 - 256: a weight of 1 is 0xFFFF00
 
 // shared-memory map (offsets from a 1024-byte aligned base)
 constexpr uint32_t kOffB = 0;
 constexpr uint32_t kOffA = kOffB + 2 * kBHalfBytes;
 constexpr uint32_t kOffV = kOffA + 2 * kABufBytes;
-constexpr uint32_t kOffPlanes = kOffV + kG * kVSlots * kVSlotBytes;
-constexpr uint32_t kOffQ = kOffPlanes + kEpiWarps * kPlaneBytes;
-constexpr uint32_t kOffXch = kOffQ + kG * 128 * 4;            // [head][tile parity][warp] (max z, max y)
-constexpr uint32_t kOffSum = kOffXch + kG * 2 * 4 * 8;        // [head][warp] partial denominators
-constexpr uint32_t kOffBar = kOffSum + kG * 4 * 4;
-// barriers: V full/empty per (head, slot), table full/empty x2, W full/empty x3, D full per head,
-// max-exchange x2 per head, planes-ready per head, [P;Q] ready
+constexpr uint32_t kOffK = kOffV + kVSlots * kUnitBytes;
+constexpr uint32_t kOffPlanes = kOffK + kKSlots * kUnitBytes;
+constexpr uint32_t kOffRef = kOffPlanes + (kEpiWarps / 2) * kPlaneBytes;  // [head][tile parity][warp] reference max y of the planes
+constexpr uint32_t kOffSum = kOffRef + kG * 2 * 4 * 4;        // [head][warp] (max z, denominator) at the end
+constexpr uint32_t kOffBar = kOffSum + kG * 4 * 8;
+// barriers: V and K full/empty per ring slot, table full/empty x2, W full/empty x3, per head: D
+// full, planes ready; [P;Q] ready
 constexpr int kBarVFull = 0;
-constexpr int kBarVEmpty = kBarVFull + kG * kVSlots;
-constexpr int kBarAFull = kBarVEmpty + kG * kVSlots;
+constexpr int kBarKFull = kBarVFull + kVSlots;
+constexpr int kBarVEmpty = kBarKFull + kKSlots;
+constexpr int kBarKEmpty = kBarVEmpty + kVSlots;
+constexpr int kBarAFull = kBarKEmpty + kKSlots;
 constexpr int kBarAEmpty = kBarAFull + 2;
 constexpr int kBarWFull = kBarAEmpty + 2;
 constexpr int kBarWEmpty = kBarWFull + kWBufs;
 constexpr int kBarDFull = kBarWEmpty + kWBufs;
-constexpr int kBarXch = kBarDFull + kG;
-constexpr int kBarPlanes = kBarXch + 2 * kG;
+constexpr int kBarPlanes = kBarDFull + kG;
 constexpr int kBarPq = kBarPlanes + kG;
 constexpr int kNumBars = kBarPq + 1;
-constexpr uint32_t kOffTmemSlot = kOffBar + kNumBars * 8;
+constexpr uint32_t kOffTmemSlot = kOffBar + 2 * kNumBars * 8;  // two sets of barriers, used by alternate items
 constexpr uint32_t kSmemBytes = kOffTmemSlot + 16;  // the dynamic shared-memory base is 1024-byte aligned
 static_assert(kOffA % 1024 == 0 && kOffV % 1024 == 0 && kOffPlanes % 256 == 0 && kOffBar % 8 == 0, "alignment");
 
@@ -99,6 +121,9 @@ __device__ unsigned int g_status = 0;
 // ------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
+__device__ __forceinline__ void mbar_inval(uint32_t bar) {
+  asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
@@ -114,6 +139,10 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 // try_wait with a suspend-time hint: the waiting thread is parked by the hardware until
 // the phase completes or the hint (ns) expires, instead of spinning on issue slots.
 constexpr uint32_t kWaitHintNs = 20000;
+#ifndef WSVD_SPIN_SLEEP_NS
+#define WSVD_SPIN_SLEEP_NS 32
+#endif
+constexpr uint32_t kSpinSleepNs = WSVD_SPIN_SLEEP_NS;
 __device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -134,8 +163,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   const uint64_t t0 = global_ns();
   for (;;) {
 #pragma unroll 1
-    for (int i = 0; i < 256; ++i)
+    for (int i = 0; i < 256; ++i) {
       if (mbar_try(bar, parity)) return true;
+      __nanosleep(kSpinSleepNs);  // leave the issue slots to the warps this one is waiting for
+    }
     if (global_ns() - t0 > 2000000000ull) return false;
   }
 }
@@ -218,32 +249,20 @@ __device__ __forceinline__ float fast_log2(float x) {
   return y;
 }
 
-// packed fp32 pairs (sm_100)
-__device__ __forceinline__ uint64_t pk(float x, float y) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(x), "f"(y));
-  return r;
-}
-__device__ __forceinline__ void upk(uint64_t v, float& x, float& y) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(x), "=f"(y) : "l"(v));
-}
-__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
-  uint64_t d;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
-// Four int8 packed in `w` (already XORed with 0x80808080) -> two fp32 pairs holding the
-// exact signed values: byte -> low mantissa of 2^23, then subtract 2^23 + 128.
-__device__ __forceinline__ void cvt4(uint32_t w, uint64_t& lo, uint64_t& hi) {
+// Four int8 packed in `w` (already XORed with 0x80808080) -> two fp32 pairs holding the exact
+// signed values: byte -> low mantissa of 2^23, then subtract 2^23 + 128.  Packed fp32 arithmetic
+// (sm_100 float2 intrinsics): the compiler keeps the pairs in aligned register pairs.
+__device__ __forceinline__ void cvt4(uint32_t w, float2& lo, float2& hi) {
   const uint32_t magic = 0x4B000000u;
-  const uint64_t bias = pk(-8388736.f, -8388736.f);
-  lo = add2(pk(__uint_as_float(__byte_perm(w, magic, 0x7650)), __uint_as_float(__byte_perm(w, magic, 0x7651))), bias);
-  hi = add2(pk(__uint_as_float(__byte_perm(w, magic, 0x7652)), __uint_as_float(__byte_perm(w, magic, 0x7653))), bias);
+  const float2 bias = make_float2(-8388736.f, -8388736.f);
+  lo = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(w, magic, 0x7650)), __uint_as_float(__byte_perm(w, magic, 0x7651))), bias);
+  hi = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(w, magic, 0x7652)), __uint_as_float(__byte_perm(w, magic, 0x7653))), bias);
+}
+
+// Byte offset, inside one head's part of a half-tile slot, of 16-byte chunk c of token tok (0..63):
+// rows of 64 bytes with the 64-byte swizzle (chunk index XOR (tok/2)%4).
+__device__ __forceinline__ uint32_t latent_off(int tok, int c) {
+  return (uint32_t)(tok * 64 + ((c ^ ((tok >> 1) & 3)) << 4));
 }
 
 // UMMA shared-memory descriptors (sm_100 descriptor version 1).
@@ -288,10 +307,13 @@ __device__ __forceinline__ uint32_t instr_desc_i8(int m, int n) {
 struct TcArgs {
   KArgs k;
   int32_t table_rows;
-  int32_t use_tma;        // 0: V rows are gathered with cp.async
-  int32_t slot_axis;      // 1 or 2: which coordinate of tmap_v is the token slot
-  alignas(64) CUtensorMap tmap_v;      // V latents as a 3-D byte tensor, box 64 bytes x 64 slots, 64-byte swizzle
-  alignas(64) CUtensorMap tmap_table;  // [2][rows][64] f16, box 64 x 128 x 1, 128-byte swizzle
+  int32_t use_tma;        // 0: latent rows are gathered with cp.async
+  int32_t slot_axis;      // 1 or 2: which coordinate of tmap_k / tmap_v is the token slot
+  int32_t box_heads;      // KV heads one tensor copy fetches: up to 4 (head-major caches), else 1
+  const int4* cta_plan;   // balanced mode: per CTA (sequence, head group, tile, number of tiles); null: split mode
+  alignas(64) CUtensorMap tmap_k;      // latents as 3-D byte tensors: box 64 bytes x 64 slots x box_heads,
+  alignas(64) CUtensorMap tmap_v;      // 64-byte swizzle
+  alignas(64) CUtensorMap tmap_table;  // [2][rows][64] f16, box 64 x 128 x 2 (cos and sin tile), 128-byte swizzle
 };
 
 // ------------------------------------------------------------------ position table
@@ -306,24 +328,76 @@ __global__ void rope_table_kernel(__half* table, int rows, KArgs a) {
   table[((size_t)rows + pos) * 64 + i] = __float2half_rn(sn);
 }
 
+// ------------------------------------------------------------------ balanced work plan
+// One CTA.  prefix[b] = tiles of 128 positions in sequences 0..b-1 (prefix[batch] = all); the
+// tile list has n_hg * prefix[batch] entries ordered by (sequence, head group, tile).  It is cut
+// into prefix[batch + 1] = min(n_ctas, entries) shares, so that no share is empty; CTA c owns
+// entries [share_begin(c), share_begin(c + 1)), and cta_plan[c] = where the share starts and how
+// many tiles it has (none for the CTAs beyond the number of shares).
+__global__ void __launch_bounds__(1024) balance_plan_kernel(const int32_t* __restrict__ b_seq_len, int batch, int n_hg,
+                                                            int n_ctas, int32_t* prefix, int4* cta_plan) {
+  __shared__ int warp_tot[32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int carry = 0;
+  for (int base = 0; base < batch; base += 1024) {
+    const int i = base + tid;
+    const int n = i < batch ? b_seq_len[i] : 0;
+    const int v = n > 0 ? (n + kTile - 1) / kTile : 0;
+    int incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      int w = warp_tot[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, w, o);
+        if (lane >= o) w += up;
+      }
+      warp_tot[lane] = w;
+    }
+    __syncthreads();
+    if (i < batch) prefix[i] = carry + (warp > 0 ? warp_tot[warp - 1] : 0) + incl - v;
+    carry += warp_tot[31];
+    __syncthreads();
+  }
+  const int64_t total = (int64_t)carry * n_hg;
+  const int shares = (int)min((int64_t)n_ctas, total);
+  if (tid == 0) {
+    prefix[batch] = carry;
+    prefix[batch + 1] = shares;
+  }
+  __syncthreads();  // the prefix sums written by this block are visible to all of its threads
+  for (int c = tid; c < n_ctas; c += 1024) {
+    int4 w = make_int4(0, 0, 0, 0);
+    if (c < shares) {
+      const int64_t begin = share_begin(c, total, shares), end = share_begin(c + 1, total, shares);
+      // the sequence that holds entry `begin`: the last b with n_hg * prefix[b] <= begin
+      int lo = 0, hi = batch;  // invariant: n_hg * prefix[lo] <= begin < n_hg * prefix[hi]
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if ((int64_t)prefix[mid] * n_hg <= begin) lo = mid; else hi = mid;
+      }
+      const int tiles_b = prefix[lo + 1] - prefix[lo];
+      const int64_t rem = begin - (int64_t)prefix[lo] * n_hg;
+      w = make_int4(lo, (int)(rem / tiles_b), (int)(rem % tiles_b), (int)(end - begin));
+    }
+    cta_plan[c] = w;
+  }
+}
+
 // ------------------------------------------------------------------ stage 1
 __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_constant__ TcArgs ta) {
   const KArgs& a = ta.k;
   const WsvdLatentDecodeParams& p = a.p;
-  const int split = blockIdx.x, hg = blockIdx.y, b = blockIdx.z;
-  const int n = p.b_seq_len[b];
-  const int lo = split * a.split_len;
-  const int hi = min(n, lo + a.split_len);
-  if (hi <= lo) return;  // empty split writes nothing
-  const int h0 = hg * kG;
-  const int G = min(kG, p.n_q_heads - h0);
-  const int npairs = (G + 1) >> 1;
-  const int ntiles = (hi - lo + kTile - 1) / kTile;
-  const int n_units = (hi - lo + kHalf - 1) / kHalf;  // half-tiles that hold at least one token
   const int gqa = p.n_q_heads / p.n_kv_heads;
   const int Rk = p.rank_k, Rv = p.rank_v;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int pos0 = (p.pos_offset != nullptr ? p.pos_offset[b] : 0) + lo;  // RoPE position of token lo
+  const int n_hg = (p.n_q_heads + kG - 1) / kG;
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t sbase = smem_u32(smem_raw);
@@ -332,67 +406,101 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
     if (threadIdx.x == 0) atomicMax(&g_status, (unsigned)kBadSmemAlignment);
     return;
   }
-  const uint32_t sB = sbase + kOffB, sA = sbase + kOffA, sV = sbase + kOffV, sPl = sbase + kOffPlanes;
-  float* qs = reinterpret_cast<float*>(sm + kOffQ);
-  const uint32_t bars = sbase + kOffBar;
+  const uint32_t sB = sbase + kOffB, sA = sbase + kOffA, sV = sbase + kOffV, sK = sbase + kOffK;
+  const uint32_t sPl = sbase + kOffPlanes;
+  uint32_t bars = sbase + kOffBar;
   auto bar = [&](int i) { return bars + 8u * i; };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + kOffTmemSlot);
-
-  const int32_t* page = p.req_to_token + (int64_t)p.b_req_idx[b] * p.rtt_stride;
-
   // 16-byte vector loads of wk need f16 data with 16-byte aligned rows
   const bool wk_vec = p.wk_dtype == WSVD_F16 && (p.wk_stride_r & 7) == 0 &&
                       (reinterpret_cast<uintptr_t>(p.wk) & 15) == 0;
-  uint4 wpre[8];
-  // requested during set-up so that their latency is hidden behind it
-  int slot_n = -1, pe0 = -1, pe1 = -1, pfirst = 0;
-  unsigned short sk_raw = 0, sv_raw = 0;
-  uint4 kreg[4];
-#pragma unroll
-  for (int c = 0; c < 4; ++c) kreg[c] = make_uint4(0u, 0u, 0u, 0u);
 
-  // ---- set-up: barriers + tensor memory (MMA warp), scaled q to shared memory (epilogue warps)
+  // ---- once per CTA: tensor memory, descriptor prefetch
   if (warp == kMmaWarp) {
-    for (int i = lane; i < kNumBars; i += 32) {
-      uint32_t count = 1;                                    // one TMA or commit arrival
-      if (i < kBarVEmpty) count = 32;                        // V full: one arrive per copying lane
-      else if (i >= kBarWEmpty && i < kBarDFull) count = 8;  // W empty: 8 warp arrivals (see w_empty_arrivals)
-      else if (i >= kBarXch && i < kBarPq) count = 4;        // the head's four warps
-      else if (i == kBarPq) count = 4 * G;
-      mbar_init(bar(i), count);
-    }
-    if (lane == 0)
-      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&ta.tmap_table)) : "memory");
-    fence_barrier_init();
-    __syncwarp();
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
     tmem_relinquish();
     tc_fence_before();
-  } else if (warp > kMmaWarp) {
-    if (ta.use_tma && lane == 0)
-      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&ta.tmap_v)) : "memory");
-    // page entries of this producer's first unit (same indexing as fetch_entries below)
-    const int nu = warp - kMmaWarp - 1;
-    if (nu < n_units) {
-      const int s0 = lo + (nu >> 1) * kTile + (nu & 1) * kHalf, sa = s0 + 2 * lane;
-      if (sa < hi) pe0 = page[sa];
-      if (sa + 1 < hi) pe1 = page[sa + 1];
-      pfirst = page[s0];
+  } else if (warp > kMmaWarp && lane == 0) {
+    if (warp == kMmaWarp + 1)
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&ta.tmap_table)) : "memory");
+    if (ta.use_tma)
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(warp == kMmaWarp + 1 ? &ta.tmap_k : &ta.tmap_v))
+                   : "memory");
+  }
+  uint32_t tmem = 0;
+
+  // ---- this CTA's work: every thread walks the same items (uniform loads, no broadcast needed)
+  const bool balanced = ta.cta_plan != nullptr;
+  int b, hg, t_first, tiles_left, split = 0;
+  if (balanced) {
+    const int4 w = ta.cta_plan[blockIdx.x];
+    b = w.x, hg = w.y, t_first = w.z, tiles_left = w.w;
+  } else {
+    split = blockIdx.x % a.n_splits, hg = (blockIdx.x / a.n_splits) % n_hg, b = blockIdx.x / (a.n_splits * n_hg);
+    t_first = 0, tiles_left = 1;
+  }
+  // The barriers of an item are re-made for the next one.  Two sets are used in turn, so that a set
+  // is invalidated and re-initialised a whole item after its last use.
+  for (int round = 0; tiles_left > 0 && b < p.batch; ++round) {
+  const int n = p.b_seq_len[b];
+  int lo, hi;
+  if (balanced) {
+    const int tiles_b = (n + kTile - 1) / kTile;
+    const int seg = min(tiles_left, tiles_b - t_first);
+    lo = t_first * kTile;
+    hi = min(n, (t_first + seg) * kTile);
+    tiles_left -= seg;
+  } else {
+    lo = split * a.split_len;
+    hi = min(n, lo + a.split_len);
+    tiles_left = 0;
+  }
+  if (hi <= lo) break;  // an empty split writes nothing (a balanced share never holds an empty item)
+  bars = sbase + kOffBar + (round & 1) * (kNumBars * 8);
+  const int h0 = hg * kG;
+  const int G = min(kG, p.n_q_heads - h0);
+  const int npairs = (G + 1) >> 1;
+  const int ntiles = (hi - lo + kTile - 1) / kTile;
+  const int n_units = (hi - lo + kHalf - 1) / kHalf;  // half-tiles that hold at least one token
+  const int pos0 = (p.pos_offset != nullptr ? p.pos_offset[b] : 0) + lo;  // RoPE position of token lo
+
+  const int32_t* page = p.req_to_token + (int64_t)p.b_req_idx[b] * p.rtt_stride;
+
+  int run_breaks = 0;
+#pragma unroll 4
+  for (int i = threadIdx.x; i + 1 < hi - lo; i += kThreads) run_breaks |= page[lo + i + 1] - page[lo + i] - 1;
+
+  uint4 wpre[8], qpre[2];
+  // requested during set-up so that their latency is hidden behind it
+  int slot_n = -1, slot_lo = 0;
+  bool affine = false;
+  unsigned short sk_raw = 0, sv_raw = 0;
+
+  // ---- set-up of the item: barriers (MMA warp), first loads (the others)
+  if (warp == kMmaWarp) {
+    for (int i = lane; i < kNumBars; i += 32) {
+      if (round >= 2) mbar_inval(bar(i));
+      uint32_t count = 1;                                    // one TMA or commit arrival
+      if (i < kBarVEmpty) count = 32;                        // V/K full: one arrive per lane of the copying warp
+      else if (i < kBarKEmpty) count = 2 * G;                // V empty: the two warps per head that own the half-tile
+      else if (i < kBarAFull) count = 2 * G;                 // K empty: the two warps per head that own the half-tile
+      else if (i >= kBarWEmpty && i < kBarDFull) count = 8;  // W empty: 8 warp arrivals (see w_empty_arrivals)
+      else if (i >= kBarPlanes && i < kBarPq) count = 4;     // planes ready: the head's four warps
+      else if (i == kBarPq) count = 4 * G;
+      mbar_init(bar(i), count);
     }
+    fence_barrier_init();
+  } else if (warp > kMmaWarp) {
+    slot_lo = page[lo];
   } else if (warp < 4 * G) {
     const int hk_pre = (h0 + (warp >> 2)) / gqa;
     {
-      // this lane's first token: page entry, K row, scales; and the page entry of its next token
+      // this lane's first token: page entry and scales; and the page entry of its next token
       const int s_first = lo + (warp & 3) * 32 + lane;
       int slot0 = -1;
       if (s_first < hi) slot0 = page[s_first];
       if (s_first + kTile < hi) slot_n = page[s_first + kTile];
       if (slot0 >= 0) {
-        const uint8_t* krow = reinterpret_cast<const uint8_t*>(p.latent_k) + (int64_t)hk_pre * p.k_stride_h +
-                              (int64_t)slot0 * p.k_stride_t;
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-          if (c * 16 < Rk) kreg[c] = __ldg(reinterpret_cast<const uint4*>(krow) + c);
         sk_raw = reinterpret_cast<const unsigned short*>(p.k_scale)[(int64_t)hk_pre * p.ks_stride_h + (int64_t)slot0 * p.ks_stride_t];
         sv_raw = reinterpret_cast<const unsigned short*>(p.v_scale)[(int64_t)hk_pre * p.vs_stride_h + (int64_t)slot0 * p.vs_stride_t];
       }
@@ -412,45 +520,32 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
         }
       }
     }
-    // q * sm_scale * log2(e): scores come out in the log2 domain
-    const float qscale = a.sm_scale * 1.4426950408889634f;
-    for (int idx = threadIdx.x; idx < G * 128; idx += 128 * G) {
-      const int g = idx >> 7, d = idx & 127;
-      const __half* qp = reinterpret_cast<const __half*>(p.q) + (int64_t)b * p.q_stride_b + (int64_t)(h0 + g) * p.q_stride_h;
-      qs[idx] = __half2float(qp[d]) * qscale;
+    // the 16 query values this thread's chunk of 8 frequencies needs (two 16-byte loads)
+    {
+      const bool il = p.rope_layout == WSVD_ROPE_INTERLEAVED;
+      const int ic = threadIdx.x & 7;
+      const __half* qp = reinterpret_cast<const __half*>(p.q) + (int64_t)b * p.q_stride_b +
+                         (int64_t)(h0 + (warp >> 2)) * p.q_stride_h;
+      qpre[0] = *reinterpret_cast<const uint4*>(qp + (il ? ic * 16 : ic * 8));
+      qpre[1] = *reinterpret_cast<const uint4*>(qp + (il ? ic * 16 + 8 : 64 + ic * 8));
     }
-    // this warp's digit planes: rows 3..7 of both chunks stay zero for the whole kernel
-    reinterpret_cast<uint2*>(sm + kOffPlanes + warp * kPlaneBytes)[lane] = make_uint2(0u, 0u);
   }
-  __syncthreads();
+  // Tensor copies need the split's token slots to be one run of consecutive slots (true for a cache
+  // laid out sequence by sequence).  Every thread compares a few neighbouring page entries (all
+  // loads independent, issued at the top of the kernel) and the barrier combines the verdicts.
+  affine = __syncthreads_and(run_breaks == 0) != 0 && ta.use_tma != 0;
   tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
+  tmem = *tmem_slot;
 
   if (warp == kMmaWarp) {
-    // ================================================================= table loads + score MMAs
+    // ================================================================= score MMAs
     if (lane == 0) {
-      auto issue_table = [&](int t) {
-        const int buf = t & 1;
-        const int row = pos0 + t * kTile;
-        mbar_expect_tx(bar(kBarAFull + buf), kABufBytes);
-        tma_load_3d(sA + buf * kABufBytes, &ta.tmap_table, 0, row, 0, bar(kBarAFull + buf));
-        tma_load_3d(sA + buf * kABufBytes + kAHalfBytes, &ta.tmap_table, 0, row, 1, bar(kBarAFull + buf));
-      };
-      issue_table(0);
-      if (ntiles > 1) issue_table(1);
       // descriptors: only the start-address field changes between k-steps, buffers and pairs
       const uint64_t adesc0 = smem_desc_sw128(sA), bdesc0 = smem_desc_sw128(sB);
       bool ok = mbar_wait(bar(kBarPq), 0);
       int u = 0;  // running count of (tile, pair) units: unit u uses W buffer u % kWBufs
       for (int t = 0; t < ntiles && ok; ++t) {
         const int buf = t & 1;
-        // The table tile of t+1 goes into the buffer MMA(t-1) read; that MMA was issued a
-        // whole iteration ago, so this wait is short and the load overlaps MMA(t).
-        if (t >= 1 && t + 1 < ntiles) {
-          ok = mbar_wait(bar(kBarAEmpty + ((t + 1) & 1)), ((t - 1) >> 1) & 1);
-          if (!ok) break;
-          issue_table(t + 1);
-        }
         ok = mbar_wait(bar(kBarAFull + buf), (t >> 1) & 1);
         for (int pr = 0; pr < npairs && ok; ++pr, ++u) {
           const int wb = u % kWBufs;
@@ -471,72 +566,135 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
         }
         if (ok) umma_commit(bar(kBarAEmpty + buf));
       }
+      // nothing may still be on its way to a barrier when the next item re-makes them: the releases
+      // of the last two table buffers are the only arrivals nobody else waits for
+      for (int t = max(0, ntiles - 2); t < ntiles && ok; ++t) ok = mbar_wait(bar(kBarAEmpty + (t & 1)), (t >> 1) & 1);
       if (!ok) atomicMax(&g_status, (unsigned)kTimeoutMma);
     }
     __syncwarp();
   } else if (warp > kMmaWarp) {
-    // ================================================================= V copies
-    // Every head's half-tiles (units n = 2*tile + half) cycle through its kVSlots ring slots; unit n
-    // is requested as soon as the value MMAs that read unit n - kVSlots have completed (their commit
-    // arrives on the slot's "empty" barrier).  Producer warp pw takes the units n = pw (mod 3).  On
-    // the TMA path lane g serves head g on its own, so the heads do not queue behind one another.
+    // ================================================================= copies, value MMAs
+    // Latent rows travel in units of half a tile (64 tokens) of all the group's KV heads; unit n =
+    // 2*tile + half uses ring slot n % kKSlots (K) or n % kVSlots (V); KV head hk0 + j sits at
+    // j * kHeadBytes inside the slot.  Warp 17 requests the table tiles and the K units: a K slot is
+    // free again once the warps that own its tokens have copied their rows to registers, at the
+    // top of the tile.  Warps 18 and 19 each serve one pair of heads (lane 0 and lane 1 one head
+    // each): they wait for the digit planes of the head's four warps, issue the head's value MMAs
+    // (one per warp of 32 tokens, each into its own 8 columns of tensor memory), wait for them to
+    // complete and tell the epilogue warps (D full); a V slot is free again once every head's MMAs
+    // on it are done, and then warp 18 requests the next odd unit and warp 19 the next even one.
     const int pw = warp - kMmaWarp - 1;
-    // page entries of the unit's 64 rows (two per lane) and of its first row
-    auto fetch_entries = [&](int nu, int& e0, int& e1, int& first) {
-      const int s0 = lo + (nu >> 1) * kTile + (nu & 1) * kHalf, sa = s0 + 2 * lane;
-      e0 = -1;
-      e1 = -1;
-      if (sa < hi) e0 = page[sa];
-      if (sa + 1 < hi) e1 = page[sa + 1];
-      first = page[s0];
-    };
-    int e0 = pe0, e1 = pe1, first = pfirst;  // unit pw's entries were requested during set-up
+    const bool is_loader = pw == 0;
+    const int hk0 = h0 / gqa, nkv = (h0 + G - 1) / gqa - hk0 + 1;  // the group's KV heads
     bool ok = true;
-    for (int nu = pw; nu < n_units && ok; nu += kProducers) {
-      int f0 = -1, f1 = -1, ffirst = 0;
-      if (nu + kProducers < n_units) fetch_entries(nu + kProducers, f0, f1, ffirst);  // one unit ahead
-      const int vslot = nu % kVSlots, use = nu / kVSlots;
-      const bool affine = (e0 < 0 || e0 == first + 2 * lane) && (e1 < 0 || e1 == first + 2 * lane + 1);
-      if (ta.use_tma && __all_sync(0xffffffffu, affine)) {
-        if (lane < G) {
-          const int stage = lane * kVSlots + vslot, hk = (h0 + lane) / gqa;
-          if (use > 0) ok = mbar_wait(bar(kBarVEmpty + stage), (use - 1) & 1);
+    // Request unit `nu` of K (is_k) or V once its ring slot is free.
+    auto load_unit = [&](int nu, bool is_k) {
+      const int nslots = is_k ? kKSlots : kVSlots;
+      const int bar_full = is_k ? kBarKFull : kBarVFull, bar_empty = is_k ? kBarKEmpty : kBarVEmpty;
+      const uint32_t ring = is_k ? sK : sV;
+      const CUtensorMap* tmap = is_k ? &ta.tmap_k : &ta.tmap_v;
+      const int R = is_k ? Rk : Rv;
+      const int64_t stride_t = is_k ? p.k_stride_t : p.v_stride_t, stride_h = is_k ? p.k_stride_h : p.v_stride_h;
+      const uint8_t* latent = reinterpret_cast<const uint8_t*>(is_k ? p.latent_k : p.latent_v);
+      const int slot = nu % nslots, use = nu / nslots;
+      if (use > 0) ok = warp_wait(bar(bar_empty + slot), (use - 1) & 1);
+      if (!ok) return;
+      const uint32_t dst = ring + slot * kUnitBytes, full = bar(bar_full + slot);
+      if (affine) {
+        // one copy for all heads, or one per KV head (lane j: head hk0 + j)
+        const int copies = ta.box_heads > 1 ? 1 : nkv;
+        if (lane < copies) {
+          const int hk = hk0 + lane, first = slot_lo + nu * kHalf;
+          const int c1 = ta.slot_axis == 1 ? first : hk, c2 = ta.slot_axis == 1 ? hk : first;
+          mbar_expect_tx(full, ta.box_heads * kHeadBytes);
+          tma_load_3d(dst + lane * kHeadBytes, tmap, 0, c1, c2, full);
+        }
+        if (lane == 0) mbar_arrive_n(full, 32 - copies);  // the arrivals the gather path makes lane by lane
+      } else {
+        // Gather through the page table, head after head: lane (r0 = lane/4, c = lane%4) copies
+        // 16-byte chunk c of rows r0 + 8k to where the tensor copy would have placed it.  Rows past
+        // the end and chunks past the rank are zero-filled.
+        const int c = lane & 3, r0 = lane >> 2;
+        const bool c_on = c * 16 < R;
+        const int s0 = lo + nu * kHalf + r0;
+        int64_t sl[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) sl[k] = (c_on && s0 + 8 * k < hi) ? page[s0 + 8 * k] : -1;
+        for (int j = 0; j < nkv; ++j) {
+          const uint8_t* base = latent + (int64_t)(hk0 + j) * stride_h;
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            cp_async16(dst + j * kHeadBytes + latent_off(r0 + 8 * k, c),
+                       base + (sl[k] >= 0 ? c * 16 + sl[k] * stride_t : 0), sl[k] >= 0 ? 16u : 0u);
+        }
+        cp_async_arrive_noinc(full);
+      }
+    };
+    if (is_loader) {
+      auto issue_table = [&](int t) {
+        if (lane == 0) {
+          const int buf = t & 1;
+          mbar_expect_tx(bar(kBarAFull + buf), kABufBytes);
+          tma_load_3d(sA + buf * kABufBytes, &ta.tmap_table, 0, pos0 + t * kTile, 0, bar(kBarAFull + buf));
+        }
+      };
+      // start: table tiles 0 and 1, K of tile 0 (units 0, 1), V of tiles 0 and 1 (units 0..3)
+      if (0 < n_units) load_unit(0, true);
+      issue_table(0);
+      if (1 < n_units) load_unit(1, true);
+      for (int nu = 0; nu < kVSlots && nu < n_units; ++nu) load_unit(nu, false);
+      if (ntiles > 1) issue_table(1);
+      for (int t = 0; t < ntiles && ok; ++t) {
+        // In the order in which their slots come free during tile t: the table tile of t+2 (the
+        // score MMAs of tile t have read its buffer), the K units of tile t+1 (tile t's rows were
+        // copied to registers at the top of the tile), the V units of tile t+1 (tile t-1's rows
+        // were handed back when its value sums were folded in, in the middle of tile t).
+        if (t + 2 < ntiles) {
+          ok = warp_wait(bar(kBarAEmpty + (t & 1)), (t >> 1) & 1);
+          if (!ok) break;
+          issue_table(t + 2);
+        }
+        if (2 * t + 2 < n_units) load_unit(2 * t + 2, true);
+        if (2 * t + 3 < n_units && ok) load_unit(2 * t + 3, true);
+        if (t >= 1) {
+          if (2 * t + 2 < n_units && ok) load_unit(2 * t + 2, false);
+          if (2 * t + 3 < n_units && ok) load_unit(2 * t + 3, false);
+        }
+      }
+    } else if (2 * (pw - 1) < G) {
+      // Value MMAs of one pair of heads: lane 0 and lane 1 one head each.
+      const int g = 2 * (pw - 1) + lane;
+      const bool agent = lane < 2 && g < G;
+      const int sub = agent ? (h0 + g) / gqa - hk0 : 0;
+      const uint32_t idesc = instr_desc_i8(64, 8);
+      const uint64_t vdesc0 = smem_desc_mn_sw64(sV + sub * kHeadBytes);
+      const uint64_t pdesc0 = smem_desc_k_plain(sPl + 2 * g * kPlaneBytes);
+      const uint32_t d_tmem = tmem + kTmemD + 32 * g;
+      for (int t = 0; t < ntiles && ok; ++t) {
+        if (agent) {
+          const int n0 = 2 * t, n1 = 2 * t + 1;
+          const int sl0 = n0 % kVSlots, sl1 = n1 % kVSlots;
+          const bool two = n1 < n_units;
+          // the V rows arrive long before the planes are ready: wait for them first, off the
+          // critical path from "planes ready" to "D full"
+          ok = mbar_wait(bar(kBarVFull + sl0), (n0 / kVSlots) & 1);
+          if (ok && two) ok = mbar_wait(bar(kBarVFull + sl1), (n1 / kVSlots) & 1);
+          if (ok) ok = mbar_wait(bar(kBarPlanes + g), t & 1);
           if (ok) {
-            const int c1 = ta.slot_axis == 1 ? first : hk, c2 = ta.slot_axis == 1 ? hk : first;
-            mbar_expect_tx(bar(kBarVFull + stage), kVSlotBytes);
-            tma_load_3d(sV + stage * kVSlotBytes, &ta.tmap_v, 0, c1, c2, bar(kBarVFull + stage));
-            mbar_arrive_n(bar(kBarVFull + stage), 31);  // the arrivals the gather path makes lane by lane
+            tc_fence_after();
+#pragma unroll
+            for (int w4 = 0; w4 < 4; ++w4) {
+              if (w4 >= 2 && !two) break;
+              const uint32_t voff = (w4 < 2 ? sl0 : sl1) * kUnitBytes + (w4 & 1) * 2048;
+              umma_i8(d_tmem + 8 * w4, vdesc0 + (voff >> 4), pdesc0 + (((w4 >> 1) * kPlaneBytes) >> 4), idesc, 0);
+            }
+            // completion of the MMAs tells the epilogue warps (D full); they in turn hand the V
+            // slots back once they have seen it
+            umma_commit(bar(kBarDFull + g));
           }
         }
         ok = __all_sync(0xffffffffu, ok);
-      } else {
-        // Gather through the page table, head after head: lane (r0 = lane/4, c = lane%4) copies
-        // 16-byte chunk c of rows r0 + 8k, placed as the 64-byte swizzle places it: chunk index
-        // XOR (row/2)%4, which does not depend on k.  Rows past the end and chunks past rank_v
-        // are zero-filled.
-        const int c = lane & 3, r0 = lane >> 2;
-        const uint32_t doff = r0 * 64 + ((c ^ ((r0 >> 1) & 3)) << 4);
-        const bool c_on = c * 16 < Rv;
-        const int s0 = lo + (nu >> 1) * kTile + (nu & 1) * kHalf + r0;
-        for (int g = 0; g < G; ++g) {
-          const int stage = g * kVSlots + vslot, hk = (h0 + g) / gqa;
-          if (use > 0) ok = mbar_wait(bar(kBarVEmpty + stage), (use - 1) & 1);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          const uint8_t* vbase = reinterpret_cast<const uint8_t*>(p.latent_v) + (int64_t)hk * p.v_stride_h;
-          const uint32_t dst = sV + stage * kVSlotBytes;
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const bool valid = c_on && s0 + 8 * k < hi;
-            const int64_t sl = valid ? page[s0 + 8 * k] : 0;
-            cp_async16(dst + doff + k * 512, vbase + (valid ? c * 16 + sl * p.v_stride_t : 0), valid ? 16u : 0u);
-          }
-          cp_async_arrive_noinc(bar(kBarVFull + stage));
-        }
       }
-      e0 = f0;
-      e1 = f1;
-      first = ffirst;
     }
     if (!ok) atomicMax(&g_status, (unsigned)kTimeoutProducer);
   } else if (warp < 4 * G) {
@@ -550,8 +708,26 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
     // ---- B operand: P (cos coefficients) and Q (sin coefficients) of this head, f16,
     //      rows n = g*64 + r, 64 frequencies per row, 128-byte swizzle; rows r >= rank_k are zero
     {
-      const float* qg = qs + g * 128;
       const int tid = threadIdx.x & 127;
+      // q * sm_scale * log2(e) (scores come out in the log2 domain): qlo[e] pairs with dimension
+      // d0 and qhi[e] with its rotation partner d1 of frequency ic*8 + e
+      float qlo[8], qhi[8];
+      {
+        const float qscale = a.sm_scale * 1.4426950408889634f;
+        const __half* q0 = reinterpret_cast<const __half*>(&qpre[0]);
+        const __half* q1 = reinterpret_cast<const __half*>(&qpre[1]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          if (interleaved) {
+            const __half* src = e < 4 ? q0 : q1;
+            qlo[e] = __half2float(src[(2 * e) & 7]) * qscale;
+            qhi[e] = __half2float(src[(2 * e + 1) & 7]) * qscale;
+          } else {
+            qlo[e] = __half2float(q0[e]) * qscale;
+            qhi[e] = __half2float(q1[e]) * qscale;
+          }
+        }
+      }
       const int64_t col = (int64_t)hk * 128;
       if (wk_vec && !interleaved) {
         // Common case (f16 wk, half-split pairing): packed f16 arithmetic.  The operands are
@@ -561,18 +737,11 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
         const int ic = tid & 7;
         __half2 qa[4], qb[4], nqa[4];
         {
-          const float4 a0 = *reinterpret_cast<const float4*>(qg + ic * 8);
-          const float4 a1 = *reinterpret_cast<const float4*>(qg + ic * 8 + 4);
-          const float4 b0 = *reinterpret_cast<const float4*>(qg + 64 + ic * 8);
-          const float4 b1 = *reinterpret_cast<const float4*>(qg + 64 + ic * 8 + 4);
-          qa[0] = __floats2half2_rn(a0.x, a0.y);
-          qa[1] = __floats2half2_rn(a0.z, a0.w);
-          qa[2] = __floats2half2_rn(a1.x, a1.y);
-          qa[3] = __floats2half2_rn(a1.z, a1.w);
-          qb[0] = __floats2half2_rn(b0.x, b0.y);
-          qb[1] = __floats2half2_rn(b0.z, b0.w);
-          qb[2] = __floats2half2_rn(b1.x, b1.y);
-          qb[3] = __floats2half2_rn(b1.z, b1.w);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            qa[e] = __floats2half2_rn(qlo[2 * e], qlo[2 * e + 1]);
+            qb[e] = __floats2half2_rn(qhi[2 * e], qhi[2 * e + 1]);
+          }
 #pragma unroll
           for (int e = 0; e < 4; ++e) nqa[e] = __hneg2(qa[e]);
         }
@@ -639,139 +808,164 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
         __align__(16) __half qv[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          const int i = ic * 8 + e;
-          const int d0 = interleaved ? 2 * i : i, d1 = interleaved ? 2 * i + 1 : i + 64;
-          pv[e] = __float2half_rn(qg[d0] * u0[e] + qg[d1] * u1[e]);
-          qv[e] = __float2half_rn(qg[d1] * u0[e] - qg[d0] * u1[e]);
+          pv[e] = __float2half_rn(qlo[e] * u0[e] + qhi[e] * u1[e]);
+          qv[e] = __float2half_rn(qhi[e] * u0[e] - qlo[e] * u1[e]);
         }
         const int nrow = g * 64 + r;
         const uint32_t off = nrow * 128 + ((ic ^ (nrow & 7)) << 4);
         *reinterpret_cast<uint4*>(sm + kOffB + off) = *reinterpret_cast<const uint4*>(pv);
         *reinterpret_cast<uint4*>(sm + kOffB + kBHalfBytes + off) = *reinterpret_cast<const uint4*>(qv);
       }
-      fence_proxy_async();  // also covers the zeroed digit planes
+      fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(kBarPq));
     }
 
-    const uint8_t* kbase = reinterpret_cast<const uint8_t*>(p.latent_k) + (int64_t)hk * p.k_stride_h;
     const __half* ksc = reinterpret_cast<const __half*>(p.k_scale) + (int64_t)hk * p.ks_stride_h;
     const __half* vsc = reinterpret_cast<const __half*>(p.v_scale) + (int64_t)hk * p.vs_stride_h;
-    float2* xch = reinterpret_cast<float2*>(sm + kOffXch) + g * 8;  // [tile parity][warp]
-    const uint32_t my_planes = sPl + warp * kPlaneBytes + (lane >> 4) * 128 + (lane & 15);
+    float* refs = reinterpret_cast<float*>(sm + kOffRef) + g * 8;  // [tile parity][warp]: max y the warp's planes refer to
+    // Digit planes: the two warps of a half-tile share one 8-row block (the MMA's B operand has 8
+    // rows): rows 0..2 hold the even warp's digits, rows 3..5 the odd warp's.  Each warp's MMA reads
+    // the whole block, so its columns 3..5 (or 0..2) are the other warp's weights times this warp's
+    // V rows: garbage that nobody reads.  Rows 6 and 7 are never written.
+    const uint32_t my_planes = sPl + (2 * g + (q4 >> 1)) * kPlaneBytes + (lane >> 4) * 128 + (q4 & 1) * 48 + (lane & 15);
+    const int sub = hk - h0 / gqa;  // this head's KV head inside a unit
     // A W buffer serves the two pairs in turn and its "empty" barrier always counts 8 warp
     // arrivals: the four warps of a pair that holds a single head arrive twice each.
     const uint32_t w_empty_arrivals = (G - 2 * pr) >= 2 ? 1u : 2u;
 
-    // running state: m_run / l_lane for the softmax denominator (reference: max z so far),
-    // big_m / acc for the value sum (reference: max y so far); lanes 0..15 of warp q4 hold rank 16*q4 + lane
-    float m_run = -INFINITY, l_lane = 0.f, big_m = -INFINITY, acc = 0.f, my_prev = -INFINITY;
+    // Running state.  Softmax denominator: l_lane under this warp's own running max m_run of z.
+    // Value sum: lanes 0..15 hold rank 16*q4 + lane of the whole head (all four warps' tokens): acc
+    // under the running reference big_m (max y of every (tile, warp) folded in so far).
+    float m_run = -INFINITY, l_lane = 0.f, big_m = -INFINITY, acc = 0.f;
     bool ok = true;
-    const uint32_t d_addr = tmem + ((uint32_t)(q4 * 32) << 16) + kTmemD + 8 * g;
-    auto fold_values = [&](float my_tile) {
-      // D[rank][0..2]: the three digit-plane sums of the tile whose max y was my_tile
-      uint32_t d[4];
-      tmem_ld4(d_addr, d);
+    const uint32_t d_addr = tmem + ((uint32_t)(q4 * 32) << 16) + kTmemD + 32 * g;
+    // Fold in the value sums of tile tp: D[rank][8*w + 0..2] are the three digit-plane sums over the
+    // 32 tokens of warp w, whose weights were taken relative to refs[tp & 1][w].
+    auto fold_values = [&](int tp) {
+      uint32_t d[4][4];
+#pragma unroll
+      for (int w4 = 0; w4 < 4; ++w4) tmem_ld4(d_addr + 8 * w4 + 3 * (w4 & 1), d[w4]);
+      const float4 rf = *reinterpret_cast<const float4*>(refs + (tp & 1) * 4);
+      const float ref[4] = {rf.x, rf.y, rf.z, rf.w};
       tmem_wait_ld();
-      if (my_tile > -INFINITY) {
-        const float v = fmaf((float)(int32_t)d[2], 65536.f, fmaf((float)(int32_t)d[1], 256.f, (float)(int32_t)d[0])) *
-                        (1.f / kPlaneScale);
-        const float m_new = fmaxf(big_m, my_tile);
-        acc = acc * fast_exp2(big_m - m_new) + v * fast_exp2(my_tile - m_new);  // big_m = -inf -> factor 0
+      float m_new = big_m;
+#pragma unroll
+      for (int w4 = 0; w4 < 4; ++w4) m_new = fmaxf(m_new, ref[w4]);
+      if (m_new > -INFINITY) {
+        acc *= fast_exp2(big_m - m_new);  // big_m = -inf -> factor 0
+#pragma unroll
+        for (int w4 = 0; w4 < 4; ++w4) {
+          if (ref[w4] > -INFINITY) {  // (a warp without tokens in this tile has no MMA and reference -inf)
+            const float v = fmaf((float)(int32_t)d[w4][2], 65536.f,
+                                 fmaf((float)(int32_t)d[w4][1], 256.f, (float)(int32_t)d[w4][0]));
+            acc = fmaf(v, fast_exp2(ref[w4] - m_new) * (1.f / kPlaneScale), acc);
+          }
+        }
         big_m = m_new;
       }
     };
 
+    unsigned short sk_n = 0, sv_n = 0;
     for (int t = 0; t < ntiles; ++t) {
       const int s = lo + t * kTile + row;
       const bool valid = s < hi;
       const int u = t * npairs + pr, wb = u % kWBufs;
+      // ---- the next tile's scales and the page entry of the tile after it: requested a whole
+      //      tile before they are used
+      sk_n = 0;
+      sv_n = 0;
+      if (slot_n >= 0) {
+        sk_n = reinterpret_cast<const unsigned short*>(ksc)[(int64_t)slot_n * p.ks_stride_t];
+        sv_n = reinterpret_cast<const unsigned short*>(vsc)[(int64_t)slot_n * p.vs_stride_t];
+      }
+      slot_n = -1;
+      if (s + 2 * kTile < hi) slot_n = page[s + 2 * kTile];
+      // ---- this warp's 32 K rows (lane = token) go from the ring slot to registers at once and
+      //      the slot is handed back: its refill has the whole tile to arrive
+      uint4 kreg[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) kreg[c] = make_uint4(0u, 0u, 0u, 0u);
+      {
+        const int nth = 2 * t + (q4 >> 1);  // this warp's tokens lie in half-tile q4/2 of the tile
+        if (nth < n_units) {
+          const int kslot = nth % kKSlots;
+          ok = warp_wait(bar(kBarKFull + kslot), (nth / kKSlots) & 1);
+          if (!ok) break;
+          const uint32_t krows = sK + kslot * kUnitBytes + sub * kHeadBytes;
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(kreg[c].x), "=r"(kreg[c].y), "=r"(kreg[c].z), "=r"(kreg[c].w)
+                         : "r"(krows + latent_off(row & (kHalf - 1), c)));
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(kBarKEmpty + kslot));
+        }
+      }
       ok = warp_wait(bar(kBarWFull + wb), (u / kWBufs) & 1);
       if (!ok) break;
       tc_fence_after();
 
       // ---- score: dot of this token's int8 K row with its row of W, 16 ranks at a time
       const uint32_t taddr = tmem + ((uint32_t)(q4 * 32) << 16) + wb * 128 + (g & 1) * kRkMax;
-      uint64_t dot[2] = {0ull, 0ull};
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t w[16];
-        tmem_ld16(taddr + c * 16, w);
-        tmem_wait_ld();
-        const uint4 kq = kreg[c];
+      float2 dot0 = make_float2(0.f, 0.f), dot1 = make_float2(0.f, 0.f);
+      // two 16-column loads in flight alternately: the next chunk of W travels while this one is used
+      uint32_t wa[16], wb16[16];
+      auto mac16 = [&](const uint32_t (&w)[16], const uint4 kq) {
         const uint32_t kws[4] = {kq.x ^ 0x80808080u, kq.y ^ 0x80808080u, kq.z ^ 0x80808080u, kq.w ^ 0x80808080u};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          uint64_t x01, x23;
+          float2 x01, x23;
           cvt4(kws[j], x01, x23);
-          dot[0] = fma2(x01, pk(__uint_as_float(w[4 * j]), __uint_as_float(w[4 * j + 1])), dot[0]);
-          dot[1] = fma2(x23, pk(__uint_as_float(w[4 * j + 2]), __uint_as_float(w[4 * j + 3])), dot[1]);
+          dot0 = __ffma2_rn(x01, make_float2(__uint_as_float(w[4 * j]), __uint_as_float(w[4 * j + 1])), dot0);
+          dot1 = __ffma2_rn(x23, make_float2(__uint_as_float(w[4 * j + 2]), __uint_as_float(w[4 * j + 3])), dot1);
         }
-      }
+      };
+      tmem_ld16(taddr, wa);
+      tmem_wait_ld();
+      tmem_ld16(taddr + 16, wb16);
+      mac16(wa, kreg[0]);
+      tmem_wait_ld();
+      tmem_ld16(taddr + 32, wa);
+      mac16(wb16, kreg[1]);
+      tmem_wait_ld();
+      tmem_ld16(taddr + 48, wb16);
+      mac16(wa, kreg[2]);
+      tmem_wait_ld();
+      mac16(wb16, kreg[3]);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_n(bar(kBarWEmpty + wb), w_empty_arrivals);  // this warp has read its rows of W
-      float d0, d1;
-      upk(add2(dot[0], dot[1]), d0, d1);
+      const float2 dsum = __fadd2_rn(dot0, dot1);
       const float sk = __half2float(__ushort_as_half(sk_raw)), sv = __half2float(__ushort_as_half(sv_raw));
-      const float z = valid ? (d0 + d1) * sk : -INFINITY;
+      const float z = valid ? (dsum.x + dsum.y) * sk : -INFINITY;
       const float y = (valid && sv > 0.f) ? z + fast_log2(sv) : -INFINITY;
+      sk_raw = sk_n;
+      sv_raw = sv_n;
 
-      // ---- the K row is consumed: fetch the next tile's row, scales and the page entry after that
-      {
-        const int sn = s + kTile;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) kreg[c] = make_uint4(0u, 0u, 0u, 0u);
-        sk_raw = 0;
-        sv_raw = 0;
-        if (sn < hi) {
-          const uint4* krow = reinterpret_cast<const uint4*>(kbase + (int64_t)slot_n * p.k_stride_t);
-#pragma unroll
-          for (int c = 0; c < 4; ++c)
-            if (c * 16 < Rk) kreg[c] = __ldg(krow + c);
-          sk_raw = reinterpret_cast<const unsigned short*>(ksc)[(int64_t)slot_n * p.ks_stride_t];
-          sv_raw = reinterpret_cast<const unsigned short*>(vsc)[(int64_t)slot_n * p.vs_stride_t];
-        }
-        slot_n = -1;
-        if (sn + kTile < hi) slot_n = page[sn + kTile];
-      }
-
-      // ---- tile maxima of z and y over the head's 128 tokens: per warp, then through shared memory
+      // ---- softmax denominator under this warp's own running max (fp32, by the owner threads)
       const float mz_w = warp_max_redux(z), my_w = warp_max_redux(y);
-      if (lane == 0) {
-        xch[(t & 1) * 4 + q4] = make_float2(mz_w, my_w);
-        mbar_arrive(bar(kBarXch + 2 * g + (t & 1)));
-      }
-      ok = warp_wait(bar(kBarXch + 2 * g + (t & 1)), (t >> 1) & 1);
-      if (!ok) break;
-      float mz = -INFINITY, my = -INFINITY;
-#pragma unroll
-      for (int w4 = 0; w4 < 4; ++w4) {
-        const float2 e = xch[(t & 1) * 4 + w4];
-        mz = fmaxf(mz, e.x);
-        my = fmaxf(my, e.y);
+      if (mz_w > -INFINITY) {
+        const float m_new = fmaxf(m_run, mz_w);
+        l_lane = l_lane * fast_exp2(m_run - m_new) + (valid ? fast_exp2(z - m_new) : 0.f);  // m_run = -inf -> factor 0
+        m_run = m_new;
       }
 
       // ---- the previous tile's value sums are in tensor memory by now: fold them in.  This also
-      //      orders every reader of D (and, through the MMA's completion, of the digit planes) before
-      //      the planes of this tile are written and before its MMAs are issued.
+      //      orders this warp's reads of D and of the references (and, through the MMAs' completion,
+      //      the MMAs' reads of its digit planes) before the planes of this tile are written.
       if (t > 0) {
         ok = warp_wait(bar(kBarDFull + g), (t - 1) & 1);
         if (!ok) break;
         tc_fence_after();
-        fold_values(my_prev);
+        fold_values(t - 1);
+        // the value MMAs of tile t-1 are complete: its V rows (this warp's half-tile) may be replaced
+        if (lane == 0 && 2 * (t - 1) + (q4 >> 1) < n_units) mbar_arrive(bar(kBarVEmpty + (2 * (t - 1) + (q4 >> 1)) % kVSlots));
       }
-      my_prev = my;
 
-      // ---- softmax denominator (fp32, by the owner threads)
+      // ---- this token's weight for the value MMA, relative to the warp's largest, as three 8-bit digits
       {
-        const float m_new = fmaxf(m_run, mz);  // finite: the tile holds at least one token
-        l_lane = l_lane * fast_exp2(m_run - m_new) + (valid ? fast_exp2(z - m_new) : 0.f);
-        m_run = m_new;
-      }
-      // ---- this token's weight for the value MMA as three 8-bit digits
-      {
-        const float w = y > -INFINITY ? fast_exp2(y - my) : 0.f;  // <= 1
+        const float w = y > -INFINITY ? fast_exp2(y - my_w) : 0.f;  // <= 1
         const uint32_t nq = __float2uint_rn(w * kPlaneScale);
         asm volatile("st.shared.u8 [%0], %1;" ::"r"(my_planes), "r"(nq) : "memory");
         asm volatile("st.shared.u8 [%0], %1;" ::"r"(my_planes + 16), "r"(nq >> 8) : "memory");
@@ -779,68 +973,61 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       }
       fence_proxy_async();
       tc_fence_before();
+      if (lane == 0) refs[(t & 1) * 4 + q4] = my_w;
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(bar(kBarPlanes + g));
-        if (q4 == 0) {
-          // ---- the head's value MMAs for this tile: one per warp of 32 tokens
-          ok = mbar_wait(bar(kBarPlanes + g), t & 1);
-          const int n0 = 2 * t, n1 = 2 * t + 1;
-          const int st0 = g * kVSlots + n0 % kVSlots, st1 = g * kVSlots + n1 % kVSlots;
-          if (ok) ok = mbar_wait(bar(kBarVFull + st0), (n0 / kVSlots) & 1);
-          if (ok && n1 < n_units) ok = mbar_wait(bar(kBarVFull + st1), (n1 / kVSlots) & 1);
-          if (ok) {
-            tc_fence_after();
-            const uint32_t idesc = instr_desc_i8(64, 8);
-            const uint32_t d_tmem = tmem + kTmemD + 8 * g;
-#pragma unroll
-            for (int w4 = 0; w4 < 4; ++w4) {
-              if (w4 >= 2 && n1 >= n_units) break;
-              const uint32_t va = sV + (w4 < 2 ? st0 : st1) * kVSlotBytes + (w4 & 1) * 2048;
-              umma_i8(d_tmem, smem_desc_mn_sw64(va), smem_desc_k_plain(sPl + (4 * g + w4) * kPlaneBytes), idesc,
-                      w4 > 0);
-            }
-            umma_commit(bar(kBarDFull + g));
-            umma_commit(bar(kBarVEmpty + st0));
-            if (n1 < n_units) umma_commit(bar(kBarVEmpty + st1));
-          }
-        }
-      }
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      if (lane == 0) mbar_arrive(bar(kBarPlanes + g));
     }
     // ---- the last tile's value sums
     if (ok) {
       ok = warp_wait(bar(kBarDFull + g), (ntiles - 1) & 1);
       if (ok) {
         tc_fence_after();
-        fold_values(my_prev);
+        fold_values(ntiles - 1);
       }
     }
     if (!ok) atomicMax(&g_status, (unsigned)kTimeoutEpilogue);
 
-    // ---- the head's denominator: sum over its four warps (all use the same reference m_run)
+    // ---- the head's denominator: the four warps' (max z, sum) pairs under a common maximum
     const float l_w = warp_sum(l_lane);
-    float* sums = reinterpret_cast<float*>(sm + kOffSum) + g * 4;
-    if (lane == 0) sums[q4] = l_w;
+    float2* sums = reinterpret_cast<float2*>(sm + kOffSum) + g * 4;
+    if (lane == 0) sums[q4] = make_float2(m_run, l_w);
     asm volatile("bar.sync %0, %1;" ::"r"(1 + g), "r"(128) : "memory");
-    const float l_tot = (sums[0] + sums[1]) + (sums[2] + sums[3]);
-    const int64_t slot = ((int64_t)b * p.n_q_heads + h) * a.n_splits + split;
+    float m_all = -INFINITY;
+#pragma unroll
+    for (int w4 = 0; w4 < 4; ++w4) m_all = fmaxf(m_all, sums[w4].x);
+    float l_tot = 0.f;
+#pragma unroll
+    for (int w4 = 0; w4 < 4; ++w4)
+      if (sums[w4].x > -INFINITY) l_tot = fmaf(sums[w4].y, fast_exp2(sums[w4].x - m_all), l_tot);
+    const int64_t slot = balanced ? ((int64_t)b * n_hg + hg + blockIdx.x) * kG + g
+                                  : ((int64_t)b * p.n_q_heads + h) * a.n_splits + split;
     const int r = 16 * q4 + lane;
     if (lane < 16 && r < Rv) {
-      // sum_s 2^z sv Lv / sum_s 2^z  =  acc * 2^(big_m - m_run) / l
-      const float o = big_m > -INFINITY ? acc * fast_exp2(big_m - m_run) / l_tot : 0.f;
+      // sum_s 2^z sv Lv / sum_s 2^z  =  acc * 2^(big_m - m_all) / l
+      const float o = big_m > -INFINITY ? acc * fast_exp2(big_m - m_all) / l_tot : 0.f;
       a.mid_o[slot * Rv + r] = o;
     }
     // natural-log lse, as the merge kernel expects (stage1.py:216)
-    if (q4 == 0 && lane == 0) a.lse[slot] = m_run * 0.6931471805599453f + logf(l_tot);
+    if (q4 == 0 && lane == 0) a.lse[slot] = m_all * 0.6931471805599453f + logf(l_tot);
   }
+
+  // ---- end of the item: every role is done with the barriers, the rings and the tensor memory
+  tc_fence_before();
+  __syncthreads();
+  // the next item of the share: the next head group, or the next sequence that has tokens
+  t_first = 0;
+  if (++hg == n_hg) {
+    hg = 0;
+    do ++b; while (b < p.batch && p.b_seq_len[b] <= 0);
+  }
+  }  // items
 
   // ---- common exit
   tc_fence_before();
   __syncthreads();
   if (warp == kMmaWarp) {
     tc_fence_after();
+    if (tmem == 0) tmem = *tmem_slot;  // no item was processed
     tmem_dealloc(tmem, kTmemCols);
   }
 }
@@ -865,16 +1052,19 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// The V latents [T, Hkv, Rv] int8 with byte strides (st, sh) as a 3-D tensor map whose outer axes
-// are ordered by stride; box = 64 bytes x 64 token slots x 1 head.  The box is wider than the
-// tensor when rank_v < 64: the missing bytes arrive as zeros.
-bool encode_v(CUtensorMap* map, const void* base, int64_t st, int64_t sh, int64_t T, int Hkv, int R, int* slot_axis) {
+// One latent tensor [T, Hkv, R] int8 with byte strides (st, sh) as a 3-D tensor map whose outer
+// axes are ordered by stride; box = 64 bytes x 64 token slots x `heads` KV heads (head-major caches,
+// where a head's 64 rows then sit together in shared memory) or x 1 head.  The box is wider than the
+// tensor when the rank is below 64, and may reach past the last head: the missing bytes arrive as zeros.
+bool encode_latent(CUtensorMap* map, const void* base, int64_t st, int64_t sh, int64_t T, int Hkv, int R, int heads,
+                   int* slot_axis) {
   EncodeTiledFn fn = encode_fn();
   if (!fn || T <= 0 || T > 0xffffffffll) return false;
   const bool slot_first = st <= sh;  // head-major storage: the slot axis has the smaller stride
+  if (!slot_first) heads = 1;
   cuuint64_t dims[3] = {(cuuint64_t)R, (cuuint64_t)(slot_first ? T : Hkv), (cuuint64_t)(slot_first ? Hkv : T)};
   cuuint64_t strides[2] = {(cuuint64_t)(slot_first ? st : sh), (cuuint64_t)(slot_first ? sh : st)};
-  cuuint32_t box[3] = {64, (cuuint32_t)(slot_first ? kHalf : 1), (cuuint32_t)(slot_first ? 1 : kHalf)};
+  cuuint32_t box[3] = {64, (cuuint32_t)(slot_first ? kHalf : 1), (cuuint32_t)(slot_first ? heads : kHalf)};
   cuuint32_t estr[3] = {1, 1, 1};
   *slot_axis = slot_first ? 1 : 2;
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
@@ -883,14 +1073,15 @@ bool encode_v(CUtensorMap* map, const void* base, int64_t st, int64_t sh, int64_
   return r == CUDA_SUCCESS;
 }
 
-// The position table [2][rows][64] f16; box = one 128-position tile of one plane, 128-byte swizzle
-// (the K-major operand layout of the score MMA).  Rows past the table read as zeros.
+// The position table [2][rows][64] f16; box = one 128-position tile of both planes (cos tile, then
+// sin tile), 128-byte swizzle (the K-major operand layout of the score MMA).  Rows past the table
+// read as zeros.
 bool encode_table(CUtensorMap* map, const void* table, int rows) {
   EncodeTiledFn fn = encode_fn();
   if (!fn || rows <= 0) return false;
   cuuint64_t dims[3] = {64, (cuuint64_t)rows, 2};
   cuuint64_t strides[2] = {128, (cuuint64_t)rows * 128};
-  cuuint32_t box[3] = {64, (cuuint32_t)kTile, 1};
+  cuuint32_t box[3] = {64, (cuuint32_t)kTile, 2};
   cuuint32_t estr[3] = {1, 1, 1};
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(table), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -908,7 +1099,15 @@ cudaError_t launch_rope_table(void* table, int rows, const KArgs& a, cudaStream_
   return cudaGetLastError();
 }
 
-cudaError_t launch_stage1_tc(const KArgs& a, const void* table, int table_rows, cudaStream_t stream) {
+cudaError_t launch_balance_plan(const int32_t* b_seq_len, int batch, int n_hg, int n_ctas, int32_t* prefix,
+                                void* cta_plan, cudaStream_t stream) {
+  tc::balance_plan_kernel<<<1, 1024, 0, stream>>>(b_seq_len, batch, n_hg, n_ctas, prefix,
+                                                  reinterpret_cast<int4*>(cta_plan));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_stage1_tc(const KArgs& a, const void* table, int table_rows, const void* cta_plan, int n_ctas,
+                             cudaStream_t stream) {
   static_assert(tc::kSmemBytes <= 232448, "shared memory budget");
   cudaError_t e = cudaFuncSetAttribute(tc::stage1_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)tc::kSmemBytes);
@@ -918,17 +1117,27 @@ cudaError_t launch_stage1_tc(const KArgs& a, const void* table, int table_rows, 
   ta.table_rows = table_rows;
   ta.use_tma = 0;
   ta.slot_axis = 1;
+  ta.box_heads = 1;
+  memset(&ta.tmap_k, 0, sizeof(CUtensorMap));
   memset(&ta.tmap_v, 0, sizeof(CUtensorMap));
   if (!tc::encode_table(&ta.tmap_table, table, table_rows)) return cudaErrorInvalidValue;
   if (a.p.n_token_slots > 0) {
-    int ax = 1;
-    if (tc::encode_v(&ta.tmap_v, a.p.latent_v, a.p.v_stride_t, a.p.v_stride_h, a.p.n_token_slots, a.p.n_kv_heads,
-                     a.p.rank_v, &ax)) {
-      ta.slot_axis = ax;
+    // KV heads one group of 4 query heads can touch (its first head is a multiple of 4)
+    const int gqa = a.p.n_q_heads / a.p.n_kv_heads;
+    const int heads = gqa == 1 ? 4 : gqa == 2 ? 2 : gqa % 4 == 0 ? 1 : 2;
+    int ax_k = 1, ax_v = 1;
+    if (tc::encode_latent(&ta.tmap_k, a.p.latent_k, a.p.k_stride_t, a.p.k_stride_h, a.p.n_token_slots,
+                          a.p.n_kv_heads, a.p.rank_k, heads, &ax_k) &&
+        tc::encode_latent(&ta.tmap_v, a.p.latent_v, a.p.v_stride_t, a.p.v_stride_h, a.p.n_token_slots,
+                          a.p.n_kv_heads, a.p.rank_v, heads, &ax_v) &&
+        ax_k == ax_v) {
+      ta.slot_axis = ax_k;
       ta.use_tma = 1;
+      ta.box_heads = ax_k == 1 ? heads : 1;
     }
   }
-  dim3 grid(a.n_splits, (a.p.n_q_heads + tc::kG - 1) / tc::kG, a.p.batch);
+  ta.cta_plan = reinterpret_cast<const int4*>(cta_plan);
+  const int grid = cta_plan != nullptr ? n_ctas : a.n_splits * ((a.p.n_q_heads + tc::kG - 1) / tc::kG) * a.p.batch;
   tc::stage1_tc_kernel<<<grid, tc::kThreads, tc::kSmemBytes, stream>>>(ta);
   return cudaGetLastError();
 }
