@@ -73,6 +73,14 @@ constexpr int kEpiWarps = 4 * kG;
 constexpr int kMmaWarp = kEpiWarps;
 constexpr int kProducers = 3;  // with the MMA warp they fill one warp slot per scheduler
 constexpr int kThreads = (kEpiWarps + 1 + kProducers) * 32;
+// Registers per thread after the two groups have re-balanced them.  The pool is the CTA's own: what
+// the control warpgroup hands back, (96 - 64) * 128, is exactly what the epilogue warpgroups take,
+// (104 - 96) * 512.  (A request the pool cannot satisfy would block for ever.)
+constexpr int kLaunchRegs = 96;  // what 640 threads per CTA leave the compiler
+constexpr int kEpiRegs = 104;
+constexpr int kCtlRegs = 64;
+static_assert((kLaunchRegs - kCtlRegs) * 4 * 32 >= (kEpiRegs - kLaunchRegs) * kEpiWarps * 32, "register pool");
+static_assert(kProducers == 3, "the control warps must form one warpgroup (4 warps) for setmaxnreg");
 constexpr int kKSlots = 2;     // half-tiles of K per head: copied to registers at the top of their tile
 constexpr int kVSlots = 4;     // half-tiles of V: the tile whose value MMAs are pending, and the next tile in flight
 constexpr int kWBufs = 3;      // W accumulators of 128 columns (one pair of heads each)
@@ -390,8 +398,11 @@ __global__ void __launch_bounds__(1024) balance_plan_kernel(const int32_t* __res
   }
 }
 
-// ------------------------------------------------------------------ stage 1
-__global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_constant__ TcArgs ta) {
+// The walk over this CTA's work items, for the epilogue warps (kEpi) or for the four control warps.
+// Two instantiations, because the two groups run with different register budgets (see the kernel):
+// everything a group executes after its setmaxnreg has to be code of its own.
+template <bool kEpi>
+__device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
   const KArgs& a = ta.k;
   const WsvdLatentDecodeParams& p = a.p;
   const int gqa = p.n_q_heads / p.n_kv_heads;
@@ -399,13 +410,7 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_hg = (p.n_q_heads + kG - 1) / kG;
 
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
-  const uint32_t sbase = smem_u32(smem_raw);
-  uint8_t* sm = smem_raw;
-  if ((sbase & 1023u) != 0) {  // the swizzled operand tiles need a 1024-byte aligned base
-    if (threadIdx.x == 0) atomicMax(&g_status, (unsigned)kBadSmemAlignment);
-    return;
-  }
+  const uint32_t sbase = smem_u32(sm);
   const uint32_t sB = sbase + kOffB, sA = sbase + kOffA, sV = sbase + kOffV, sK = sbase + kOffK;
   const uint32_t sPl = sbase + kOffPlanes;
   uint32_t bars = sbase + kOffBar;
@@ -415,20 +420,7 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
   const bool wk_vec = p.wk_dtype == WSVD_F16 && (p.wk_stride_r & 7) == 0 &&
                       (reinterpret_cast<uintptr_t>(p.wk) & 15) == 0;
 
-  // ---- once per CTA: tensor memory, descriptor prefetch
-  if (warp == kMmaWarp) {
-    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
-    tmem_relinquish();
-    tc_fence_before();
-  } else if (warp > kMmaWarp && lane == 0) {
-    if (warp == kMmaWarp + 1)
-      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&ta.tmap_table)) : "memory");
-    if (ta.use_tma)
-      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(warp == kMmaWarp + 1 ? &ta.tmap_k : &ta.tmap_v))
-                   : "memory");
-  }
   uint32_t tmem = 0;
-
   // ---- this CTA's work: every thread walks the same items (uniform loads, no broadcast needed)
   const bool balanced = ta.cta_plan != nullptr;
   int b, hg, t_first, tiles_left, split = 0;
@@ -477,6 +469,7 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
   unsigned short sk_raw = 0, sv_raw = 0;
 
   // ---- set-up of the item: barriers (MMA warp), first loads (the others)
+  if constexpr (!kEpi) {
   if (warp == kMmaWarp) {
     for (int i = lane; i < kNumBars; i += 32) {
       if (round >= 2) mbar_inval(bar(i));
@@ -490,9 +483,11 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       mbar_init(bar(i), count);
     }
     fence_barrier_init();
-  } else if (warp > kMmaWarp) {
+  } else {
     slot_lo = page[lo];
-  } else if (warp < 4 * G) {
+  }
+  } else {
+  if (warp < 4 * G) {
     const int hk_pre = (h0 + (warp >> 2)) / gqa;
     {
       // this lane's first token: page entry and scales; and the page entry of its next token
@@ -530,6 +525,7 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       qpre[1] = *reinterpret_cast<const uint4*>(qp + (il ? ic * 16 + 8 : 64 + ic * 8));
     }
   }
+  }
   // Tensor copies need the split's token slots to be one run of consecutive slots (true for a cache
   // laid out sequence by sequence).  Every thread compares a few neighbouring page entries (all
   // loads independent, issued at the top of the kernel) and the barrier combines the verdicts.
@@ -537,6 +533,7 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
   tc_fence_after();
   tmem = *tmem_slot;
 
+  if constexpr (!kEpi) {
   if (warp == kMmaWarp) {
     // ================================================================= score MMAs
     if (lane == 0) {
@@ -572,7 +569,7 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       if (!ok) atomicMax(&g_status, (unsigned)kTimeoutMma);
     }
     __syncwarp();
-  } else if (warp > kMmaWarp) {
+  } else {
     // ================================================================= copies, value MMAs
     // Latent rows travel in units of half a tile (64 tokens) of all the group's KV heads; unit n =
     // 2*tile + half uses ring slot n % kKSlots (K) or n % kVSlots (V); KV head hk0 + j sits at
@@ -697,7 +694,9 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
       }
     }
     if (!ok) atomicMax(&g_status, (unsigned)kTimeoutProducer);
-  } else if (warp < 4 * G) {
+  }
+  } else {
+  if (warp < 4 * G) {
     // ================================================================= epilogue
     const int g = warp >> 2, q4 = warp & 3;
     const int h = h0 + g, hk = h / gqa;
@@ -1010,6 +1009,7 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
     // natural-log lse, as the merge kernel expects (stage1.py:216)
     if (q4 == 0 && lane == 0) a.lse[slot] = m_all * 0.6931471805599453f + logf(l_tot);
   }
+  }
 
   // ---- end of the item: every role is done with the barriers, the rings and the tensor memory
   tc_fence_before();
@@ -1021,14 +1021,50 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
     do ++b; while (b < p.batch && p.b_seq_len[b] <= 0);
   }
   }  // items
+}
+
+// ------------------------------------------------------------------ stage 1
+__global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_constant__ TcArgs ta) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t sbase = smem_u32(smem_raw);
+  uint8_t* sm = smem_raw;
+  if ((sbase & 1023u) != 0) {  // the swizzled operand tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) atomicMax(&g_status, (unsigned)kBadSmemAlignment);
+    return;
+  }
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + kOffTmemSlot);
+
+  // ---- once per CTA: tensor memory, descriptor prefetch
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
+    tmem_relinquish();
+    tc_fence_before();
+  } else if (warp > kMmaWarp && lane == 0) {
+    if (warp == kMmaWarp + 1)
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&ta.tmap_table)) : "memory");
+    if (ta.use_tma)
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(warp == kMmaWarp + 1 ? &ta.tmap_k : &ta.tmap_v))
+                   : "memory");
+  }
+
+  // ---- register budgets.  The launch gives every thread 96 registers (640 threads); the tile loop of
+  //      the epilogue needs more and the control warps far fewer, so the control warpgroup hands
+  //      registers back to the pool and the four epilogue warpgroups take them.
+  if (warp < kEpiWarps) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kEpiRegs));
+    run_share<true>(ta, sm);
+  } else {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kCtlRegs));
+    run_share<false>(ta, sm);
+  }
 
   // ---- common exit
   tc_fence_before();
   __syncthreads();
   if (warp == kMmaWarp) {
     tc_fence_after();
-    if (tmem == 0) tmem = *tmem_slot;  // no item was processed
-    tmem_dealloc(tmem, kTmemCols);
+    tmem_dealloc(*tmem_slot, kTmemCols);
   }
 }
 
