@@ -19,8 +19,8 @@
 // slot is refilled a whole tile before its next use).
 //
 // Values.  O[r] = sum_s p_s sv_s Lv[s,r] is a true contraction over the tokens and runs on
-// the tensor cores as an int8 MMA (kind::i8): the A operand is the V half-tile exactly as
-// TMA wrote it (64 tokens x 64 bytes, 64-byte swizzle = the MN-major canonical layout), the
+// the tensor cores as an int8 MMA (kind::i8): the A operand is a quarter of the V tile exactly as
+// TMA wrote it (32 tokens x 64 bytes, 64-byte swizzle = the MN-major canonical layout), the
 // B operand is the tile's weights a_s = 2^(y_s - max y), y_s = z_s + log2 sv_s, written by
 // their owner threads as three unsigned 8-bit digit planes of round(a_s * (2^24 - 256));
 // the int32 accumulator (64 ranks x 8 columns per head) is read back once per tile and
@@ -42,17 +42,19 @@
 //    split plan, partials in the [B, Hq, n_splits] layout of the reference's stage 1.
 // 20 warps:
 //   warps 0-15   epilogue, 4 per head: warp w owns tensor-memory lanes 32*(w%4)..+31, i.e.
-//                tokens 32*(w%4).. of every tile of head w/4; lane 0 of the head's first warp
-//                issues the head's value MMAs
+//                tokens 32*(w%4).. of every tile of head w/4
 //   warp 16      one thread issues the score MMAs
-//   warp 17      requests the table tiles and the K rows
-//   warps 18-19  one pair of heads each: request the V rows, issue the pair's value MMAs
-// Latent rows travel in units of half a tile (64 tokens) of ALL the group's heads: one TMA tensor
-// copy of 16 KB (64 bytes x 64 token slots x 4 heads) when the unit's token slots are consecutive
+//   warp 17      requests the table tiles and the K and V rows
+//   warps 18-19  one pair of heads each (lane 0 and lane 1 one head each): issue the value MMAs
+// The 16 epilogue warps and the 4 control warps are two register groups: after the launch the
+// control warpgroup gives registers back and the epilogue warpgroups take them (setmaxnreg).
+// Latent rows travel in units of one tile (128 tokens) of ALL the group's heads: one TMA tensor
+// copy of 32 KB (64 bytes x 128 token slots x 4 heads) when the tile's token slots are consecutive
 // and the cache is head-major, else one copy per head, else a gather of rows with 16-byte
-// cp.async through the page table.  A thread needs several hundred cycles to wait for a slot and
-// issue one copy, whatever its size, so the copies are few and large: 5 per tile and CTA (one
-// table tile, two K units, two V units), spread over three warps.
+// cp.async through the page table.  In the busy SM a control thread needs 20-40 cycles per
+// instruction, so waiting for a slot and issuing one copy costs 600-800 cycles whatever the size
+// of the copy: with five copies per tile (half-tile units) the requesting warp, not HBM, set the
+// pace of the whole kernel.  Hence few and large copies: 3 per tile and CTA (table, K, V).
 // Every wait inside the tile loop is an mbarrier wait with a time limit; on a time-out the
 // kernel records a status code and every role falls through to the common exit, which frees
 // the tensor memory.
@@ -67,7 +69,6 @@ namespace tc {
 constexpr int kG = 4;          // heads per CTA
 static_assert(kG == kBalancedGroup, "the merge kernel indexes balanced partials by groups of kG heads");
 constexpr int kTile = 128;     // positions per MMA tile (= tensor-memory lanes)
-constexpr int kHalf = kTile / 2;
 constexpr int kRkMax = 64;
 constexpr int kEpiWarps = 4 * kG;
 constexpr int kMmaWarp = kEpiWarps;
@@ -81,12 +82,12 @@ constexpr int kEpiRegs = 104;
 constexpr int kCtlRegs = 64;
 static_assert((kLaunchRegs - kCtlRegs) * 4 * 32 >= (kEpiRegs - kLaunchRegs) * kEpiWarps * 32, "register pool");
 static_assert(kProducers == 3, "the control warps must form one warpgroup (4 warps) for setmaxnreg");
-constexpr int kKSlots = 2;     // half-tiles of K per head: copied to registers at the top of their tile
-constexpr int kVSlots = 4;     // half-tiles of V: the tile whose value MMAs are pending, and the next tile in flight
+constexpr int kKSlots = 1;     // tiles of K: a tile's rows are copied to registers at the top of the tile
+constexpr int kVSlots = 2;     // tiles of V: the tile whose value MMAs are pending, and the next tile in flight
 constexpr int kWBufs = 3;      // W accumulators of 128 columns (one pair of heads each)
 
-constexpr uint32_t kHeadBytes = kHalf * 64;         // one head's part of a unit: 64 tokens x 64 bytes (rank < 64: zero-filled)
-constexpr uint32_t kUnitBytes = kG * kHeadBytes;    // a ring slot: half a tile of K or V for up to 4 KV heads
+constexpr uint32_t kHeadBytes = kTile * 64;         // one head's part of a unit: 128 tokens x 64 bytes (rank < 64: zero-filled)
+constexpr uint32_t kUnitBytes = kG * kHeadBytes;    // a ring slot: one tile of K or V for up to 4 KV heads
 constexpr uint32_t kAHalfBytes = kTile * 128;       // 128 rows x 64 f16
 constexpr uint32_t kABufBytes = 2 * kAHalfBytes;    // cos half + sin half
 constexpr uint32_t kBHalfBytes = kG * kRkMax * 128; // 256 rows x 64 f16
@@ -267,7 +268,7 @@ __device__ __forceinline__ void cvt4(uint32_t w, float2& lo, float2& hi) {
   hi = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(w, magic, 0x7652)), __uint_as_float(__byte_perm(w, magic, 0x7653))), bias);
 }
 
-// Byte offset, inside one head's part of a half-tile slot, of 16-byte chunk c of token tok (0..63):
+// Byte offset, inside one head's part of a ring slot, of 16-byte chunk c of token tok (0..127):
 // rows of 64 bytes with the 64-byte swizzle (chunk index XOR (tok/2)%4).
 __device__ __forceinline__ uint32_t latent_off(int tok, int c) {
   return (uint32_t)(tok * 64 + ((c ^ ((tok >> 1) & 3)) << 4));
@@ -453,7 +454,6 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
   const int G = min(kG, p.n_q_heads - h0);
   const int npairs = (G + 1) >> 1;
   const int ntiles = (hi - lo + kTile - 1) / kTile;
-  const int n_units = (hi - lo + kHalf - 1) / kHalf;  // half-tiles that hold at least one token
   const int pos0 = (p.pos_offset != nullptr ? p.pos_offset[b] : 0) + lo;  // RoPE position of token lo
 
   const int32_t* page = p.req_to_token + (int64_t)p.b_req_idx[b] * p.rtt_stride;
@@ -475,8 +475,8 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
       if (round >= 2) mbar_inval(bar(i));
       uint32_t count = 1;                                    // one TMA or commit arrival
       if (i < kBarVEmpty) count = 32;                        // V/K full: one arrive per lane of the copying warp
-      else if (i < kBarKEmpty) count = 2 * G;                // V empty: the two warps per head that own the half-tile
-      else if (i < kBarAFull) count = 2 * G;                 // K empty: the two warps per head that own the half-tile
+      else if (i < kBarKEmpty) count = G;                    // V empty: one commit per head, after the head's value MMAs on the slot
+      else if (i < kBarAFull) count = 4 * G;                 // K empty: every warp that copies rows out of the slot
       else if (i >= kBarWEmpty && i < kBarDFull) count = 8;  // W empty: 8 warp arrivals (see w_empty_arrivals)
       else if (i >= kBarPlanes && i < kBarPq) count = 4;     // planes ready: the head's four warps
       else if (i == kBarPq) count = 4 * G;
@@ -571,58 +571,59 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
     __syncwarp();
   } else {
     // ================================================================= copies, value MMAs
-    // Latent rows travel in units of half a tile (64 tokens) of all the group's KV heads; unit n =
-    // 2*tile + half uses ring slot n % kKSlots (K) or n % kVSlots (V); KV head hk0 + j sits at
-    // j * kHeadBytes inside the slot.  Warp 17 requests the table tiles and the K units: a K slot is
-    // free again once the warps that own its tokens have copied their rows to registers, at the
-    // top of the tile.  Warps 18 and 19 each serve one pair of heads (lane 0 and lane 1 one head
-    // each): they wait for the digit planes of the head's four warps, issue the head's value MMAs
-    // (one per warp of 32 tokens, each into its own 8 columns of tensor memory), wait for them to
-    // complete and tell the epilogue warps (D full); a V slot is free again once every head's MMAs
-    // on it are done, and then warp 18 requests the next odd unit and warp 19 the next even one.
+    // Latent rows travel in units of one tile (128 tokens) of all the group's KV heads; tile n uses
+    // ring slot n % kKSlots (K) or n % kVSlots (V); KV head hk0 + j sits at j * kHeadBytes inside
+    // the slot.  Warp 17 requests the table tiles and the K and V tiles: a K slot is free again once
+    // every warp has copied its rows to registers, at the top of the tile; a V slot once every
+    // head's value MMAs on it are complete.  Warps 18 and 19 each serve one pair of heads (lane 0
+    // and lane 1 one head each): they wait for the digit planes of the head's four warps and issue
+    // the head's value MMAs (one per warp of 32 tokens, each into its own 8 columns of tensor
+    // memory); two commits then tell the epilogue warps (D full) and the requesting warp (V empty)
+    // when the MMAs have completed.
     const int pw = warp - kMmaWarp - 1;
     const bool is_loader = pw == 0;
     const int hk0 = h0 / gqa, nkv = (h0 + G - 1) / gqa - hk0 + 1;  // the group's KV heads
     bool ok = true;
-    // Request unit `nu` of K (is_k) or V once its ring slot is free.
+    // Request tile `nu` of K (is_k) or V once its ring slot is free.
     auto load_unit = [&](int nu, bool is_k) {
       const int nslots = is_k ? kKSlots : kVSlots;
       const int bar_full = is_k ? kBarKFull : kBarVFull, bar_empty = is_k ? kBarKEmpty : kBarVEmpty;
-      const uint32_t ring = is_k ? sK : sV;
-      const CUtensorMap* tmap = is_k ? &ta.tmap_k : &ta.tmap_v;
-      const int R = is_k ? Rk : Rv;
-      const int64_t stride_t = is_k ? p.k_stride_t : p.v_stride_t, stride_h = is_k ? p.k_stride_h : p.v_stride_h;
-      const uint8_t* latent = reinterpret_cast<const uint8_t*>(is_k ? p.latent_k : p.latent_v);
       const int slot = nu % nslots, use = nu / nslots;
       if (use > 0) ok = warp_wait(bar(bar_empty + slot), (use - 1) & 1);
       if (!ok) return;
-      const uint32_t dst = ring + slot * kUnitBytes, full = bar(bar_full + slot);
+      const uint32_t dst = (is_k ? sK : sV) + slot * kUnitBytes, full = bar(bar_full + slot);
       if (affine) {
         // one copy for all heads, or one per KV head (lane j: head hk0 + j)
         const int copies = ta.box_heads > 1 ? 1 : nkv;
         if (lane < copies) {
-          const int hk = hk0 + lane, first = slot_lo + nu * kHalf;
+          const int hk = hk0 + lane, first = slot_lo + nu * kTile;
           const int c1 = ta.slot_axis == 1 ? first : hk, c2 = ta.slot_axis == 1 ? hk : first;
           mbar_expect_tx(full, ta.box_heads * kHeadBytes);
-          tma_load_3d(dst + lane * kHeadBytes, tmap, 0, c1, c2, full);
+          tma_load_3d(dst + lane * kHeadBytes, is_k ? &ta.tmap_k : &ta.tmap_v, 0, c1, c2, full);
         }
         if (lane == 0) mbar_arrive_n(full, 32 - copies);  // the arrivals the gather path makes lane by lane
       } else {
         // Gather through the page table, head after head: lane (r0 = lane/4, c = lane%4) copies
         // 16-byte chunk c of rows r0 + 8k to where the tensor copy would have placed it.  Rows past
         // the end and chunks past the rank are zero-filled.
+        const int R = is_k ? Rk : Rv;
+        const int64_t stride_t = is_k ? p.k_stride_t : p.v_stride_t, stride_h = is_k ? p.k_stride_h : p.v_stride_h;
+        const uint8_t* latent = reinterpret_cast<const uint8_t*>(is_k ? p.latent_k : p.latent_v);
         const int c = lane & 3, r0 = lane >> 2;
         const bool c_on = c * 16 < R;
-        const int s0 = lo + nu * kHalf + r0;
-        int64_t sl[8];
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+          const int s0 = lo + nu * kTile + half * 64 + r0;
+          int64_t sl[8];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) sl[k] = (c_on && s0 + 8 * k < hi) ? page[s0 + 8 * k] : -1;
-        for (int j = 0; j < nkv; ++j) {
-          const uint8_t* base = latent + (int64_t)(hk0 + j) * stride_h;
+          for (int k = 0; k < 8; ++k) sl[k] = (c_on && s0 + 8 * k < hi) ? page[s0 + 8 * k] : -1;
+          for (int j = 0; j < nkv; ++j) {
+            const uint8_t* base = latent + (int64_t)(hk0 + j) * stride_h;
 #pragma unroll
-          for (int k = 0; k < 8; ++k)
-            cp_async16(dst + j * kHeadBytes + latent_off(r0 + 8 * k, c),
-                       base + (sl[k] >= 0 ? c * 16 + sl[k] * stride_t : 0), sl[k] >= 0 ? 16u : 0u);
+            for (int k = 0; k < 8; ++k)
+              cp_async16(dst + j * kHeadBytes + latent_off(half * 64 + r0 + 8 * k, c),
+                         base + (sl[k] >= 0 ? c * 16 + sl[k] * stride_t : 0), sl[k] >= 0 ? 16u : 0u);
+          }
         }
         cp_async_arrive_noinc(full);
       }
@@ -635,28 +636,26 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
           tma_load_3d(sA + buf * kABufBytes, &ta.tmap_table, 0, pos0 + t * kTile, 0, bar(kBarAFull + buf));
         }
       };
-      // start: table tiles 0 and 1, K of tile 0 (units 0, 1), V of tiles 0 and 1 (units 0..3)
-      if (0 < n_units) load_unit(0, true);
+      // start: K of tile 0, table tiles 0 and 1, V of tiles 0 and 1
+      load_unit(0, true);
       issue_table(0);
-      if (1 < n_units) load_unit(1, true);
-      for (int nu = 0; nu < kVSlots && nu < n_units; ++nu) load_unit(nu, false);
-      if (ntiles > 1) issue_table(1);
+      load_unit(0, false);
+      if (ntiles > 1) {
+        load_unit(1, false);
+        issue_table(1);
+      }
       for (int t = 0; t < ntiles && ok; ++t) {
         // In the order in which their slots come free during tile t: the table tile of t+2 (the
-        // score MMAs of tile t have read its buffer), the K units of tile t+1 (tile t's rows were
-        // copied to registers at the top of the tile), the V units of tile t+1 (tile t-1's rows
-        // were handed back when its value sums were folded in, in the middle of tile t).
+        // score MMAs of tile t have read its buffer), K of tile t+1 (tile t's rows were copied to
+        // registers at the top of the tile), V of tile t+1 (tile t-1's value MMAs completed shortly
+        // after the end of tile t-1).
         if (t + 2 < ntiles) {
           ok = warp_wait(bar(kBarAEmpty + (t & 1)), (t >> 1) & 1);
           if (!ok) break;
           issue_table(t + 2);
         }
-        if (2 * t + 2 < n_units) load_unit(2 * t + 2, true);
-        if (2 * t + 3 < n_units && ok) load_unit(2 * t + 3, true);
-        if (t >= 1) {
-          if (2 * t + 2 < n_units && ok) load_unit(2 * t + 2, false);
-          if (2 * t + 3 < n_units && ok) load_unit(2 * t + 3, false);
-        }
+        if (t + 1 < ntiles) load_unit(t + 1, true);
+        if (t >= 1 && t + 1 < ntiles && ok) load_unit(t + 1, false);
       }
     } else if (2 * (pw - 1) < G) {
       // Value MMAs of one pair of heads: lane 0 and lane 1 one head each.
@@ -669,25 +668,21 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
       const uint32_t d_tmem = tmem + kTmemD + 32 * g;
       for (int t = 0; t < ntiles && ok; ++t) {
         if (agent) {
-          const int n0 = 2 * t, n1 = 2 * t + 1;
-          const int sl0 = n0 % kVSlots, sl1 = n1 % kVSlots;
-          const bool two = n1 < n_units;
+          const int vslot = t % kVSlots;
           // the V rows arrive long before the planes are ready: wait for them first, off the
           // critical path from "planes ready" to "D full"
-          ok = mbar_wait(bar(kBarVFull + sl0), (n0 / kVSlots) & 1);
-          if (ok && two) ok = mbar_wait(bar(kBarVFull + sl1), (n1 / kVSlots) & 1);
+          ok = mbar_wait(bar(kBarVFull + vslot), (t / kVSlots) & 1);
           if (ok) ok = mbar_wait(bar(kBarPlanes + g), t & 1);
           if (ok) {
             tc_fence_after();
 #pragma unroll
             for (int w4 = 0; w4 < 4; ++w4) {
-              if (w4 >= 2 && !two) break;
-              const uint32_t voff = (w4 < 2 ? sl0 : sl1) * kUnitBytes + (w4 & 1) * 2048;
+              const uint32_t voff = vslot * kUnitBytes + w4 * 2048;  // the 32 tokens of warp w4: 32 rows of 64 bytes
               umma_i8(d_tmem + 8 * w4, vdesc0 + (voff >> 4), pdesc0 + (((w4 >> 1) * kPlaneBytes) >> 4), idesc, 0);
             }
-            // completion of the MMAs tells the epilogue warps (D full); they in turn hand the V
-            // slots back once they have seen it
+            // completion of the MMAs tells the epilogue warps (D full) and hands the V slot back
             umma_commit(bar(kBarDFull + g));
+            umma_commit(bar(kBarVEmpty + vslot));
           }
         }
         ok = __all_sync(0xffffffffu, ok);
@@ -823,7 +818,7 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
     const __half* ksc = reinterpret_cast<const __half*>(p.k_scale) + (int64_t)hk * p.ks_stride_h;
     const __half* vsc = reinterpret_cast<const __half*>(p.v_scale) + (int64_t)hk * p.vs_stride_h;
     float* refs = reinterpret_cast<float*>(sm + kOffRef) + g * 8;  // [tile parity][warp]: max y the warp's planes refer to
-    // Digit planes: the two warps of a half-tile share one 8-row block (the MMA's B operand has 8
+    // Digit planes: the two warps of half a tile share one 8-row block (the MMA's B operand has 8
     // rows): rows 0..2 hold the even warp's digits, rows 3..5 the odd warp's.  Each warp's MMA reads
     // the whole block, so its columns 3..5 (or 0..2) are the other warp's weights times this warp's
     // V rows: garbage that nobody reads.  Rows 6 and 7 are never written.
@@ -883,23 +878,18 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
       // ---- this warp's 32 K rows (lane = token) go from the ring slot to registers at once and
       //      the slot is handed back: its refill has the whole tile to arrive
       uint4 kreg[4];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) kreg[c] = make_uint4(0u, 0u, 0u, 0u);
       {
-        const int nth = 2 * t + (q4 >> 1);  // this warp's tokens lie in half-tile q4/2 of the tile
-        if (nth < n_units) {
-          const int kslot = nth % kKSlots;
-          ok = warp_wait(bar(kBarKFull + kslot), (nth / kKSlots) & 1);
-          if (!ok) break;
-          const uint32_t krows = sK + kslot * kUnitBytes + sub * kHeadBytes;
+        const int kslot = t % kKSlots;
+        ok = warp_wait(bar(kBarKFull + kslot), (t / kKSlots) & 1);
+        if (!ok) break;
+        const uint32_t krows = sK + kslot * kUnitBytes + sub * kHeadBytes;
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
-            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                         : "=r"(kreg[c].x), "=r"(kreg[c].y), "=r"(kreg[c].z), "=r"(kreg[c].w)
-                         : "r"(krows + latent_off(row & (kHalf - 1), c)));
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(kBarKEmpty + kslot));
-        }
+        for (int c = 0; c < 4; ++c)
+          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(kreg[c].x), "=r"(kreg[c].y), "=r"(kreg[c].z), "=r"(kreg[c].w)
+                       : "r"(krows + latent_off(row, c)));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(kBarKEmpty + kslot));
       }
       ok = warp_wait(bar(kBarWFull + wb), (u / kWBufs) & 1);
       if (!ok) break;
@@ -958,8 +948,6 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
         if (!ok) break;
         tc_fence_after();
         fold_values(t - 1);
-        // the value MMAs of tile t-1 are complete: its V rows (this warp's half-tile) may be replaced
-        if (lane == 0 && 2 * (t - 1) + (q4 >> 1) < n_units) mbar_arrive(bar(kBarVEmpty + (2 * (t - 1) + (q4 >> 1)) % kVSlots));
       }
 
       // ---- this token's weight for the value MMA, relative to the warp's largest, as three 8-bit digits
@@ -1089,8 +1077,8 @@ EncodeTiledFn encode_fn() {
 }
 
 // One latent tensor [T, Hkv, R] int8 with byte strides (st, sh) as a 3-D tensor map whose outer
-// axes are ordered by stride; box = 64 bytes x 64 token slots x `heads` KV heads (head-major caches,
-// where a head's 64 rows then sit together in shared memory) or x 1 head.  The box is wider than the
+// axes are ordered by stride; box = 64 bytes x 128 token slots x `heads` KV heads (head-major caches,
+// where a head's 128 rows then sit together in shared memory) or x 1 head.  The box is wider than the
 // tensor when the rank is below 64, and may reach past the last head: the missing bytes arrive as zeros.
 bool encode_latent(CUtensorMap* map, const void* base, int64_t st, int64_t sh, int64_t T, int Hkv, int R, int heads,
                    int* slot_axis) {
@@ -1100,7 +1088,7 @@ bool encode_latent(CUtensorMap* map, const void* base, int64_t st, int64_t sh, i
   if (!slot_first) heads = 1;
   cuuint64_t dims[3] = {(cuuint64_t)R, (cuuint64_t)(slot_first ? T : Hkv), (cuuint64_t)(slot_first ? Hkv : T)};
   cuuint64_t strides[2] = {(cuuint64_t)(slot_first ? st : sh), (cuuint64_t)(slot_first ? sh : st)};
-  cuuint32_t box[3] = {64, (cuuint32_t)(slot_first ? kHalf : 1), (cuuint32_t)(slot_first ? heads : kHalf)};
+  cuuint32_t box[3] = {64, (cuuint32_t)(slot_first ? kTile : 1), (cuuint32_t)(slot_first ? heads : kTile)};
   cuuint32_t estr[3] = {1, 1, 1};
   *slot_axis = slot_first ? 1 : 2;
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
