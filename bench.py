@@ -655,8 +655,9 @@ def main():
             "gather_check": gather_ok,
             "e2e": {"value": m.bytes_total / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "us_per_layer": ms_e2e * 1e3,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            # per step: [the kernel that cuts the tiles into per-SM shares,] stage 1, merge (+ gather)
-            "gpu_launches": args.steps * (3 if m.balanced else 2),
+            # per step: one kernel when the library balances the tiles itself on one GPU (stage 1 merges and
+            # projects in its last-arriving CTAs), else stage 1 + the merge kernel (which is also the gather)
+            "gpu_launches": args.steps * (1 if m.balanced and m.pg is None and world == 1 else 2),
             "kernel_status": int(status.item()),
             "clocks": clocks,
         }

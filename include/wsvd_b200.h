@@ -119,15 +119,18 @@ int wsvd_kernel_status_reset(void);
  * while its kernel autotunes it.  It is what runs when p->split_len > 0 and on the generic
  * kernel.  With p->split_len == 0 and a problem the tensor-core kernel accepts (head_dim 128,
  * int8 latents, ranks multiples of 16 up to 64, 16-byte aligned rows), wsvd_latent_decode does
- * not use fixed-length splits at all: it cuts the batch's tiles of 128 positions into equal
- * shares, one per SM, from the sequence lengths on the device, so that ragged batches load
- * every SM alike; the plan returned here is then only what wsvd_latent_decode_stage1 would run.
+ * not use fixed-length splits at all: one kernel, one persistent CTA per SM, cuts the batch's
+ * tiles of 128 positions into equal shares from the sequence lengths on the device (ragged
+ * batches load every SM alike), and the CTA that completes a head's last partial merges the
+ * partials, applies U_v and writes the output row, so that no merge kernel runs; the plan
+ * returned here is then only what wsvd_latent_decode_stage1 would run.
  */
 int wsvd_latent_decode_plan(const WsvdLatentDecodeParams* p, int32_t* split_len, int32_t* n_splits);
 
 /* Bytes of scratch the op needs: the partial results and their log-sum-exp in f32 (the mid_o /
- * mid_o_logexpsum tensors of flash_decoding.py:31-36), the balanced work plan where one is
- * used, and the cos/sin position table when p->rope_table is NULL.  Device independent. */
+ * mid_o_logexpsum tensors of flash_decoding.py:31-36), the tile prefix sums and arrival counters
+ * of the balanced mode, and the cos/sin position table when p->rope_table is NULL.  Device
+ * independent.  Nothing in it has to be initialised by the caller. */
 size_t wsvd_latent_decode_workspace_bytes(const WsvdLatentDecodeParams* p);
 
 /*
@@ -139,9 +142,9 @@ size_t wsvd_latent_decode_workspace_bytes(const WsvdLatentDecodeParams* p);
 int wsvd_latent_decode(const WsvdLatentDecodeParams* p, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
- * wsvd_latent_decode without its merge kernel: everything up to and including stage 1, the
- * partials left in `workspace` in the library's own layout.  For timing the dominant kernel
- * with the work distribution the whole op uses; p->out is not written and may be NULL.
+ * wsvd_latent_decode without the merge: stage 1 with the work distribution the whole op uses,
+ * the partials left in `workspace` in the library's own layout.  For timing the dominant kernel
+ * alone; p->out is not written and may be NULL.
  */
 int wsvd_latent_decode_partials(const WsvdLatentDecodeParams* p, void* workspace, size_t workspace_bytes,
                                 void* stream);

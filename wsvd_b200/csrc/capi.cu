@@ -109,9 +109,9 @@ void fill_args(const WsvdLatentDecodeParams* p, float* mid_o, float* lse, int sp
 }
 
 // `scratch_table`: where to build the position table when the caller gave none (may be null);
-// `cta_plan`: the balanced work plan for n_ctas persistent CTAs of the tensor-core kernel, or null
-// (fixed-length splits, partials in the [B, Hq, n_splits] layout).
-int run_stage1(const wsvd::KArgs& a, void* scratch_table, const void* cta_plan, int n_ctas, cudaStream_t stream) {
+// `work`: how the tensor-core kernel distributes its work (ignored by the generic kernel, which
+// always runs fixed-length splits).
+int run_stage1(const wsvd::KArgs& a, void* scratch_table, const wsvd::Stage1Work& work, cudaStream_t stream) {
   if (a.p.batch == 0) return WSVD_OK;
   const bool tc = tc_eligible(&a.p) && a.split_len % 128 == 0 && (a.p.rope_table || scratch_table);
   if (!tc) {
@@ -127,7 +127,7 @@ int run_stage1(const wsvd::KArgs& a, void* scratch_table, const void* cta_plan, 
     if (e != cudaSuccess) return cuda_fail(e);
     table = scratch_table;
   }
-  cudaError_t e = wsvd::launch_stage1_tc(a, table, rows, cta_plan, n_ctas, stream);
+  cudaError_t e = wsvd::launch_stage1_tc(a, table, rows, work, stream);
   return e == cudaSuccess ? WSVD_OK : cuda_fail(e);
 }
 
@@ -137,12 +137,13 @@ bool balanced_mode(const WsvdLatentDecodeParams* p) { return p->split_len == 0 &
 
 size_t align256(size_t b) { return (b + 255) & ~(size_t)255; }
 
-// Workspace: partials (mid_o, then lse), [balanced mode: tile prefix sums per sequence, per-CTA
-// plan,] [the position table when the caller passed none].  Sizes do not depend on the device.
+// Workspace: partials (mid_o, then lse), [balanced mode: tile prefix sums per sequence, arrival
+// counters per (sequence, head),] [the position table when the caller passed none].  Sizes do not
+// depend on the device.
 struct Layout {
-  size_t slots;       // partial results: one per (sequence, head, split) or per (item, head of the group)
-  size_t prefix_off;  // balanced mode only
-  size_t plan_off;
+  size_t slots;         // partial results: one per (sequence, head, split) or per (item, head of the group)
+  size_t prefix_off;    // balanced mode only
+  size_t arrivals_off;  // balanced mode only
   size_t table_off;
   size_t total;
 };
@@ -156,8 +157,8 @@ Layout workspace_layout(const WsvdLatentDecodeParams* p, int n_splits) {
   if (bal) {
     l.prefix_off = off;
     off += align256(((size_t)p->batch + 2) * sizeof(int32_t));
-    l.plan_off = off;
-    off += (size_t)wsvd::kMaxBalancedCtas * 16;
+    l.arrivals_off = off;
+    off += align256((size_t)p->batch * p->n_q_heads * sizeof(uint32_t));
   }
   l.table_off = off;
   if (tc_eligible(p) && !p->rope_table) off += wsvd::rope_table_bytes(table_rows_for(p->max_len));
@@ -305,18 +306,20 @@ static int decode_impl(const WsvdLatentDecodeParams* p, const WsvdPeerSet* peers
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   void* scratch_table = p->rope_table ? nullptr : ws + l.table_off;
   wsvd::PartialIndex where = {nullptr, 0, ns, sl};
-  const void* cta_plan = nullptr;
+  wsvd::Stage1Work work = {0, nullptr, nullptr};
   if (balanced_mode(p)) {
-    st = balanced_ctas(p, &where.n_ctas);
+    st = balanced_ctas(p, &work.n_ctas);
     if (st != WSVD_OK) return st;
-    where.prefix = reinterpret_cast<const int32_t*>(ws + l.prefix_off);
-    cta_plan = ws + l.plan_off;
-    const cudaError_t e = wsvd::launch_balance_plan(
-        p->b_seq_len, p->batch, (p->n_q_heads + wsvd::kBalancedGroup - 1) / wsvd::kBalancedGroup, where.n_ctas,
-        reinterpret_cast<int32_t*>(ws + l.prefix_off), ws + l.plan_off, s);
-    if (e != cudaSuccess) return cuda_fail(e);
+    where.n_ctas = work.n_ctas;
+    if (merge && !peers) {
+      // one kernel: the CTA that completes a head's last partial merges and writes the output row
+      work.arrivals = reinterpret_cast<unsigned int*>(ws + l.arrivals_off);
+      return run_stage1(a, scratch_table, work, s);
+    }
+    work.prefix = reinterpret_cast<int32_t*>(ws + l.prefix_off);
+    where.prefix = work.prefix;
   }
-  st = run_stage1(a, scratch_table, cta_plan, where.n_ctas, s);
+  st = run_stage1(a, scratch_table, work, s);
   if (st != WSVD_OK || !merge) return st;
   cudaError_t e =
       peers ? wsvd::launch_stage2_peers(mid_o, lse, p->b_seq_len, *peers, p->batch, p->n_q_heads, where, p->rank_v,
@@ -390,7 +393,7 @@ int wsvd_latent_decode_stage1(const WsvdLatentDecodeParams* p, float* mid_o, flo
   if ((long)n_splits * p->split_len < p->max_len) return WSVD_ERR_WORKSPACE_TOO_SMALL;
   wsvd::KArgs a;
   fill_args(p, mid_o, lse, p->split_len, n_splits, &a);
-  return run_stage1(a, nullptr, nullptr, 0, reinterpret_cast<cudaStream_t>(stream));
+  return run_stage1(a, nullptr, wsvd::Stage1Work{0, nullptr, nullptr}, reinterpret_cast<cudaStream_t>(stream));
 }
 
 static void dense_plan(const WsvdDenseDecodeParams* p, int* sl, int* ns) {

@@ -65,7 +65,7 @@ constexpr int kMaxBalancedCtas = 256;
 // Where the merge finds the partials.  Split mode (prefix null): [B, Hq, n_splits] slots, the first
 // ceil(len / split_len) of a row used.  Balanced mode: slot (b * n_hg + hg + c) * 4 + h % 4 for every
 // CTA c whose share holds tiles of (sequence b, head group hg); prefix[b] = tiles in sequences before
-// b, prefix[batch + 1] = number of shares (both written by the plan kernel).
+// b, prefix[batch + 1] = number of shares (both written by stage 1).
 struct PartialIndex {
   const int32_t* prefix;  // [batch + 2], or null
   int32_t n_ctas;         // CTAs of the stage-1 grid (>= the number of shares)
@@ -81,13 +81,18 @@ int record_cuda_error(cudaError_t e);
 
 // Launchers implemented in the kernel translation units.
 cudaError_t launch_stage1_generic(const KArgs& a, cudaStream_t stream);
-// `cta_plan`: the output of launch_balance_plan for a grid of n_ctas persistent CTAs (partials in the
-// balanced layout), or null: one CTA per (split, head group, sequence), partials in the split layout.
-cudaError_t launch_stage1_tc(const KArgs& a, const void* table, int table_rows, const void* cta_plan, int n_ctas,
+// How the tensor-core kernel distributes its work.  n_ctas == 0: one CTA per (split, head group,
+// sequence), partials in the split layout.  n_ctas > 0: that many persistent CTAs with equal shares
+// of the tile list, partials in the balanced layout; then either `prefix` ([batch + 2] int32, written
+// by the kernel for the merge kernel) or `arrivals` ([batch * n_q_heads] uint32, zeroed by the
+// launcher: the kernel merges, applies U_v and writes p.out itself) is given.
+struct Stage1Work {
+  int n_ctas;
+  int32_t* prefix;
+  unsigned int* arrivals;
+};
+cudaError_t launch_stage1_tc(const KArgs& a, const void* table, int table_rows, const Stage1Work& work,
                              cudaStream_t stream);
-// prefix: [batch + 2] int32; cta_plan: n_ctas x 16 bytes (16-byte aligned)
-cudaError_t launch_balance_plan(const int32_t* b_seq_len, int batch, int n_hg, int n_ctas, int32_t* prefix,
-                                void* cta_plan, cudaStream_t stream);
 cudaError_t launch_rope_table(void* table, int rows, const KArgs& a, cudaStream_t stream);
 size_t rope_table_bytes(int rows);
 cudaError_t read_tc_status(unsigned int* out);

@@ -30,14 +30,19 @@
 //
 // Work.  A work item is a run of consecutive tiles of one (sequence, group of 4 heads); it ends
 // in one partial result (normalised latent-space row + log-sum-exp per head) for the merge kernel.
-//  - Balanced mode (cta_plan given): all tiles of the batch, ordered by (sequence, head group,
-//    tile), are cut into gridDim.x equal shares, one per persistent CTA (one CTA per SM).  A share
-//    covers a few items: the tail of one (sequence, head group), whole ones, the head of another.
-//    No SM idles in a partial last wave whatever the sequence lengths, the [P;Q] build is paid
-//    once per item, and tensor memory is allocated once.  balance_plan_kernel computes the shares
-//    from the sequence lengths on the device; the partial of item (sequence b, head group hg) of
-//    CTA c goes to slot (b * n_hg + hg + c), which is unique because along the tile order every
-//    new item advances the (sequence, head group) index or the CTA index.
+//  - Balanced mode: all tiles of the batch, ordered by (sequence, head group, tile), are cut
+//    into equal shares, one per persistent CTA (one CTA per SM).  A share covers a few items: the
+//    tail of one (sequence, head group), whole ones, the head of another.  No SM idles in a
+//    partial last wave whatever the sequence lengths, the [P;Q] build is paid once per item, and
+//    tensor memory is allocated once.  Every CTA computes its share itself from the sequence
+//    lengths (a block-wide prefix sum at the start of the kernel).  The partial of item (sequence
+//    b, head group hg) of CTA c goes to slot (b * n_hg + hg + c), which is unique because along
+//    the tile order every new item advances the (sequence, head group) index or the CTA index.
+//    With arrival counters (one per (sequence, head), zeroed before the launch) the kernel is the
+//    whole op: the CTA that completes a head's last partial merges the partials, multiplies by
+//    the head's slice of U_v and writes the output row; an item that one CTA covers alone skips
+//    the partials altogether.  Without counters the partials and the prefix sums are left for
+//    the merge kernel.
 //  - Split mode (no plan): CTA blockIdx.x handles split blockIdx.x % n_splits of a fixed-length
 //    split plan, partials in the [B, Hq, n_splits] layout of the reference's stage 1.
 // 20 warps:
@@ -319,7 +324,9 @@ struct TcArgs {
   int32_t use_tma;        // 0: latent rows are gathered with cp.async
   int32_t slot_axis;      // 1 or 2: which coordinate of tmap_k / tmap_v is the token slot
   int32_t box_heads;      // KV heads one tensor copy fetches: up to 4 (head-major caches), else 1
-  const int4* cta_plan;   // balanced mode: per CTA (sequence, head group, tile, number of tiles); null: split mode
+  int32_t balanced;        // 0: split mode
+  int32_t* prefix_out;     // balanced mode: [batch + 2] tile prefix sums and share count for the merge kernel, or null
+  unsigned int* arrivals;  // balanced mode: [batch * n_q_heads] zeroed arrival counters = merge inside this kernel, or null
   alignas(64) CUtensorMap tmap_k;      // latents as 3-D byte tensors: box 64 bytes x 64 slots x box_heads,
   alignas(64) CUtensorMap tmap_v;      // 64-byte swizzle
   alignas(64) CUtensorMap tmap_table;  // [2][rows][64] f16, box 64 x 128 x 2 (cos and sin tile), 128-byte swizzle
@@ -335,68 +342,6 @@ __global__ void rope_table_kernel(__half* table, int rows, KArgs a) {
   sincosf((float)pos * a.inv_freq[i], &sn, &cs);
   table[(size_t)pos * 64 + i] = __float2half_rn(cs);
   table[((size_t)rows + pos) * 64 + i] = __float2half_rn(sn);
-}
-
-// ------------------------------------------------------------------ balanced work plan
-// One CTA.  prefix[b] = tiles of 128 positions in sequences 0..b-1 (prefix[batch] = all); the
-// tile list has n_hg * prefix[batch] entries ordered by (sequence, head group, tile).  It is cut
-// into prefix[batch + 1] = min(n_ctas, entries) shares, so that no share is empty; CTA c owns
-// entries [share_begin(c), share_begin(c + 1)), and cta_plan[c] = where the share starts and how
-// many tiles it has (none for the CTAs beyond the number of shares).
-__global__ void __launch_bounds__(1024) balance_plan_kernel(const int32_t* __restrict__ b_seq_len, int batch, int n_hg,
-                                                            int n_ctas, int32_t* prefix, int4* cta_plan) {
-  __shared__ int warp_tot[32];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  int carry = 0;
-  for (int base = 0; base < batch; base += 1024) {
-    const int i = base + tid;
-    const int n = i < batch ? b_seq_len[i] : 0;
-    const int v = n > 0 ? (n + kTile - 1) / kTile : 0;
-    int incl = v;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int up = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += up;
-    }
-    if (lane == 31) warp_tot[warp] = incl;
-    __syncthreads();
-    if (warp == 0) {
-      int w = warp_tot[lane];
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int up = __shfl_up_sync(0xffffffffu, w, o);
-        if (lane >= o) w += up;
-      }
-      warp_tot[lane] = w;
-    }
-    __syncthreads();
-    if (i < batch) prefix[i] = carry + (warp > 0 ? warp_tot[warp - 1] : 0) + incl - v;
-    carry += warp_tot[31];
-    __syncthreads();
-  }
-  const int64_t total = (int64_t)carry * n_hg;
-  const int shares = (int)min((int64_t)n_ctas, total);
-  if (tid == 0) {
-    prefix[batch] = carry;
-    prefix[batch + 1] = shares;
-  }
-  __syncthreads();  // the prefix sums written by this block are visible to all of its threads
-  for (int c = tid; c < n_ctas; c += 1024) {
-    int4 w = make_int4(0, 0, 0, 0);
-    if (c < shares) {
-      const int64_t begin = share_begin(c, total, shares), end = share_begin(c + 1, total, shares);
-      // the sequence that holds entry `begin`: the last b with n_hg * prefix[b] <= begin
-      int lo = 0, hi = batch;  // invariant: n_hg * prefix[lo] <= begin < n_hg * prefix[hi]
-      while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if ((int64_t)prefix[mid] * n_hg <= begin) lo = mid; else hi = mid;
-      }
-      const int tiles_b = prefix[lo + 1] - prefix[lo];
-      const int64_t rem = begin - (int64_t)prefix[lo] * n_hg;
-      w = make_int4(lo, (int)(rem / tiles_b), (int)(rem % tiles_b), (int)(end - begin));
-    }
-    cta_plan[c] = w;
-  }
 }
 
 // The walk over this CTA's work items, for the epilogue warps (kEpi) or for the four control warps.
@@ -423,26 +368,109 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
 
   uint32_t tmem = 0;
   // ---- this CTA's work: every thread walks the same items (uniform loads, no broadcast needed)
-  const bool balanced = ta.cta_plan != nullptr;
-  int b, hg, t_first, tiles_left, split = 0;
+  const bool balanced = ta.balanced != 0;
+  const bool fused = balanced && ta.arrivals != nullptr;
+  int b = 0, hg = 0, t_first = 0, tiles_left = 0, split = 0;
+  int before_b = 0;     // balanced mode: tiles in the sequences before b
+  int64_t total = 0;    // balanced mode: entries of the tile list
+  int shares = 0;       // balanced mode: CTAs that have a share
   if (balanced) {
-    const int4 w = ta.cta_plan[blockIdx.x];
-    b = w.x, hg = w.y, t_first = w.z, tiles_left = w.w;
+    // Tiles per sequence -> block-wide sums -> this CTA's share [begin, end) of the tile list and the
+    // (sequence, head group, tile) it starts at.  Scratch: the reference/sum area, unused until the
+    // first tile.
+    int* plan_sm = reinterpret_cast<int*>(sm + kOffRef);  // [0, 20): per-warp sums; [24], [25]: start sequence, tiles before it
+    constexpr int kWarps = kThreads / 32;
+    auto tiles_of = [&](int i) {
+      const int n = i < p.batch ? p.b_seq_len[i] : 0;
+      return n > 0 ? (n + kTile - 1) / kTile : 0;
+    };
+    int mine = 0;
+    for (int i = threadIdx.x; i < p.batch; i += kThreads) mine += tiles_of(i);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+    if (lane == 0) plan_sm[warp] = mine;
+    __syncthreads();
+    int all_tiles = 0;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) all_tiles += plan_sm[w];
+    __syncthreads();
+    total = (int64_t)all_tiles * n_hg;
+    shares = (int)min((int64_t)gridDim.x, total);
+    const bool has_share = (int)blockIdx.x < shares;
+    const int64_t begin = has_share ? share_begin(blockIdx.x, total, shares) : 0;
+    if (has_share) tiles_left = (int)(share_begin(blockIdx.x + 1, total, shares) - begin);
+    if (has_share || (blockIdx.x == 0 && ta.prefix_out != nullptr)) {
+      int carry = 0;
+      for (int base = 0; base < p.batch; base += kThreads) {
+        const int i = base + threadIdx.x;
+        const int v = tiles_of(i);
+        int incl = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int up = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += up;
+        }
+        if (lane == 31) plan_sm[warp] = incl;
+        __syncthreads();
+        int lower = 0, chunk = 0;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+          const int x = plan_sm[w];
+          if (w < warp) lower += x;
+          chunk += x;
+        }
+        const int excl = carry + lower + incl - v;
+        if (has_share && v > 0 && (int64_t)excl * n_hg <= begin && begin < (int64_t)(excl + v) * n_hg) {
+          plan_sm[24] = i;
+          plan_sm[25] = excl;
+        }
+        if (blockIdx.x == 0 && ta.prefix_out != nullptr && i < p.batch) ta.prefix_out[i] = excl;
+        carry += chunk;
+        __syncthreads();
+      }
+      if (blockIdx.x == 0 && ta.prefix_out != nullptr && threadIdx.x == 0) {
+        ta.prefix_out[p.batch] = all_tiles;
+        ta.prefix_out[p.batch + 1] = shares;
+      }
+      if (has_share) {
+        b = plan_sm[24];
+        before_b = plan_sm[25];
+        const int tiles_b = tiles_of(b);
+        const int64_t rem = begin - (int64_t)before_b * n_hg;
+        hg = (int)(rem / tiles_b);
+        t_first = (int)(rem % tiles_b);
+      }
+      __syncthreads();  // the scratch area is handed back
+    }
+    // sequences without tokens belong to no share: their output rows are zeros
+    if (fused) {
+      const int n_out = p.wv != nullptr ? p.head_dim : Rv;
+      for (int bb = blockIdx.x; bb < p.batch; bb += gridDim.x) {
+        if (p.b_seq_len[bb] > 0) continue;
+        __half* orow = reinterpret_cast<__half*>(p.out) + (int64_t)bb * p.out_stride_b;
+        for (int i = threadIdx.x; i < p.n_q_heads * n_out; i += kThreads)
+          orow[(int64_t)(i / n_out) * p.out_stride_h + i % n_out] = __float2half_rn(0.f);
+      }
+    }
   } else {
     split = blockIdx.x % a.n_splits, hg = (blockIdx.x / a.n_splits) % n_hg, b = blockIdx.x / (a.n_splits * n_hg);
-    t_first = 0, tiles_left = 1;
+    tiles_left = 1;
   }
   // The barriers of an item are re-made for the next one.  Two sets are used in turn, so that a set
   // is invalidated and re-initialised a whole item after its last use.
   for (int round = 0; tiles_left > 0 && b < p.batch; ++round) {
   const int n = p.b_seq_len[b];
   int lo, hi;
+  int tiles_b = 0, n_parts = 1, c_first = 0;  // balanced mode: the CTAs that share this (sequence, head group)
   if (balanced) {
-    const int tiles_b = (n + kTile - 1) / kTile;
+    tiles_b = (n + kTile - 1) / kTile;
     const int seg = min(tiles_left, tiles_b - t_first);
     lo = t_first * kTile;
     hi = min(n, (t_first + seg) * kTile);
     tiles_left -= seg;
+    const int64_t first = (int64_t)before_b * n_hg + (int64_t)hg * tiles_b;
+    c_first = share_owner(first, total, shares);
+    n_parts = share_owner(first + tiles_b - 1, total, shares) - c_first + 1;
   } else {
     lo = split * a.split_len;
     hi = min(n, lo + a.split_len);
@@ -989,13 +1017,68 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
     const int64_t slot = balanced ? ((int64_t)b * n_hg + hg + blockIdx.x) * kG + g
                                   : ((int64_t)b * p.n_q_heads + h) * a.n_splits + split;
     const int r = 16 * q4 + lane;
-    if (lane < 16 && r < Rv) {
-      // sum_s 2^z sv Lv / sum_s 2^z  =  acc * 2^(big_m - m_all) / l
-      const float o = big_m > -INFINITY ? acc * fast_exp2(big_m - m_all) / l_tot : 0.f;
-      a.mid_o[slot * Rv + r] = o;
+    // sum_s 2^z sv Lv / sum_s 2^z  =  acc * 2^(big_m - m_all) / l
+    const float o = big_m > -INFINITY ? acc * fast_exp2(big_m - m_all) / l_tot : 0.f;
+    const bool alone = fused && n_parts == 1;  // this CTA covered the whole (sequence, head): no partials
+    if (!alone) {
+      if (lane < 16 && r < Rv) a.mid_o[slot * Rv + r] = o;
+      // natural-log lse, as the merge kernel expects (stage1.py:216)
+      if (q4 == 0 && lane == 0) a.lse[slot] = m_all * 0.6931471805599453f + logf(l_tot);
     }
-    // natural-log lse, as the merge kernel expects (stage1.py:216)
-    if (q4 == 0 && lane == 0) a.lse[slot] = m_all * 0.6931471805599453f + logf(l_tot);
+    if (fused) {
+      // The head's merged latent-space row goes to shared memory (the head's digit-plane area: its
+      // value MMAs are complete), then the head's 128 threads apply U_v and write the output row.
+      float* o_row = reinterpret_cast<float*>(sm + kOffPlanes + 2 * g * kPlaneBytes);
+      int* verdict = reinterpret_cast<int*>(sm + kOffSum) + g * 8;  // the head's (max, sum) pairs were read above
+      bool finish = alone;
+      if (alone) {
+        if (lane < 16 && r < Rv) o_row[r] = o;
+      } else {
+        // the CTA that adds the head's last partial merges them all
+        __threadfence();
+        asm volatile("bar.sync %0, %1;" ::"r"(1 + g), "r"(128) : "memory");
+        if (q4 == 0 && lane == 0) {
+          const unsigned int seen = atomicAdd(ta.arrivals + (int64_t)b * p.n_q_heads + h, 1u);
+          __threadfence();
+          verdict[0] = seen + 1u == (unsigned int)n_parts;
+        }
+        asm volatile("bar.sync %0, %1;" ::"r"(1 + g), "r"(128) : "memory");
+        finish = verdict[0] != 0;
+        if (finish) {
+          const int64_t slot0 = ((int64_t)b * n_hg + hg + c_first) * kG + g;
+          float m = -INFINITY;
+          for (int i = 0; i < n_parts; ++i) m = fmaxf(m, __ldcg(a.lse + slot0 + (int64_t)i * kG));
+          float wsum = 0.f, osum = 0.f;
+          const int rr = q4 * 32 + lane;  // one rank per thread of the head
+          for (int i = 0; i < n_parts; ++i) {
+            const float w = __expf(__ldcg(a.lse + slot0 + (int64_t)i * kG) - m);
+            wsum += w;
+            if (rr < Rv) osum = fmaf(w, __ldcg(a.mid_o + (slot0 + (int64_t)i * kG) * Rv + rr), osum);
+          }
+          if (rr < Rv) o_row[rr] = osum / wsum;
+        }
+      }
+      if (finish) {
+        asm volatile("bar.sync %0, %1;" ::"r"(1 + g), "r"(128) : "memory");
+        __half* out = reinterpret_cast<__half*>(p.out) + (int64_t)b * p.out_stride_b + (int64_t)h * p.out_stride_h;
+        const int d = q4 * 32 + lane;
+        if (p.wv == nullptr) {
+          if (d < Rv) out[d] = __float2half_rn(o_row[d]);
+        } else {
+          // out[d] = sum_r O_lat[r] U_v[r, hk*128 + d]: consecutive d in consecutive lanes, four sums in flight
+          const __half* w = reinterpret_cast<const __half*>(p.wv) + (int64_t)hk * p.head_dim + d;
+          float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
+#pragma unroll 4
+          for (int k = 0; k < Rv; k += 4) {
+            y0 = fmaf(o_row[k], __half2float(__ldg(w + (int64_t)k * p.wv_stride_r)), y0);
+            y1 = fmaf(o_row[k + 1], __half2float(__ldg(w + (int64_t)(k + 1) * p.wv_stride_r)), y1);
+            y2 = fmaf(o_row[k + 2], __half2float(__ldg(w + (int64_t)(k + 2) * p.wv_stride_r)), y2);
+            y3 = fmaf(o_row[k + 3], __half2float(__ldg(w + (int64_t)(k + 3) * p.wv_stride_r)), y3);
+          }
+          out[d] = __float2half_rn((y0 + y1) + (y2 + y3));
+        }
+      }
+    }
   }
   }
 
@@ -1006,6 +1089,7 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
   t_first = 0;
   if (++hg == n_hg) {
     hg = 0;
+    before_b += tiles_b;
     do ++b; while (b < p.batch && p.b_seq_len[b] <= 0);
   }
   }  // items
@@ -1123,14 +1207,7 @@ cudaError_t launch_rope_table(void* table, int rows, const KArgs& a, cudaStream_
   return cudaGetLastError();
 }
 
-cudaError_t launch_balance_plan(const int32_t* b_seq_len, int batch, int n_hg, int n_ctas, int32_t* prefix,
-                                void* cta_plan, cudaStream_t stream) {
-  tc::balance_plan_kernel<<<1, 1024, 0, stream>>>(b_seq_len, batch, n_hg, n_ctas, prefix,
-                                                  reinterpret_cast<int4*>(cta_plan));
-  return cudaGetLastError();
-}
-
-cudaError_t launch_stage1_tc(const KArgs& a, const void* table, int table_rows, const void* cta_plan, int n_ctas,
+cudaError_t launch_stage1_tc(const KArgs& a, const void* table, int table_rows, const Stage1Work& work,
                              cudaStream_t stream) {
   static_assert(tc::kSmemBytes <= 232448, "shared memory budget");
   cudaError_t e = cudaFuncSetAttribute(tc::stage1_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1160,8 +1237,14 @@ cudaError_t launch_stage1_tc(const KArgs& a, const void* table, int table_rows, 
       ta.box_heads = ax_k == 1 ? heads : 1;
     }
   }
-  ta.cta_plan = reinterpret_cast<const int4*>(cta_plan);
-  const int grid = cta_plan != nullptr ? n_ctas : a.n_splits * ((a.p.n_q_heads + tc::kG - 1) / tc::kG) * a.p.batch;
+  ta.balanced = work.n_ctas > 0;
+  ta.prefix_out = work.prefix;
+  ta.arrivals = work.arrivals;
+  const int grid = work.n_ctas > 0 ? work.n_ctas : a.n_splits * ((a.p.n_q_heads + tc::kG - 1) / tc::kG) * a.p.batch;
+  if (work.n_ctas > 0 && work.arrivals != nullptr) {
+    e = cudaMemsetAsync(work.arrivals, 0, sizeof(unsigned int) * (size_t)a.p.batch * a.p.n_q_heads, stream);
+    if (e != cudaSuccess) return e;
+  }
   tc::stage1_tc_kernel<<<grid, tc::kThreads, tc::kSmemBytes, stream>>>(ta);
   return cudaGetLastError();
 }
