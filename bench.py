@@ -229,7 +229,7 @@ def run_c5(args):
             if ok.item() == 0:
                 pg = None
             else:
-                collective = ("head all-gather fused into the merge kernel (peer stores + flag barrier) per layer; "
+                collective = ("head all-gather fused into the decode kernel (peer stores + flag barrier) per layer; "
                               "nccl all_reduce of the FFN output")
     model = LatentDecoder(spec, B, context, capacity, rank=rank, world=world, device=dev, seed=5, peer_gather=pg)
     x = (torch.randn(B, spec.hidden, device=dev, dtype=torch.float32) * 0.5).to(torch.float16)
@@ -403,7 +403,8 @@ class Measurement:
                 if ok.item() == 0:
                     self.pg = None
                 else:
-                    self.collective = "fused into the merge kernel: peer stores of [B,H_local,128] f16 + flag barrier"
+                    self.collective = ("fused into the decode kernel: the CTA that completes a head stores its row into every "
+                                       "rank's gathered buffer (16-byte peer stores); the last CTA runs the flag barrier")
         # inputs smaller than ~2x the 126 MB L2 would be served from cache on repeated calls:
         # then every timed call is preceded by a write of a 512 MB buffer and timed on its own
         self.flush = (torch.empty(512 << 20, dtype=torch.uint8, device=dev)
@@ -573,7 +574,7 @@ def main():
     ap.add_argument("--shard-heads", action="store_true", help="accepted for compatibility: strong scaling is the default")
     ap.add_argument("--no-graph", action="store_true", help="c5 step: launch from Python instead of one CUDA graph")
     ap.add_argument("--collective", default="fused", choices=["fused", "nccl"],
-                    help="N>1: head all-gather fused into the merge kernel (peer stores), or an NCCL all_gather")
+                    help="N>1: head all-gather fused into the decode kernel (peer stores), or an NCCL all_gather")
     ap.add_argument("--no-dense", action="store_true", help="skip the dense f16 baseline kernel timing")
     ap.add_argument("--no-extra", action="store_true",
                     help="skip the `strong` list (c3, c4 at this N) and the reference Triton kernels")
@@ -655,9 +656,10 @@ def main():
             "gather_check": gather_ok,
             "e2e": {"value": m.bytes_total / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "us_per_layer": ms_e2e * 1e3,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            # per step: one kernel when the library balances the tiles itself on one GPU (stage 1 merges and
-            # projects in its last-arriving CTAs), else stage 1 + the merge kernel (which is also the gather)
-            "gpu_launches": args.steps * (1 if m.balanced and m.pg is None and world == 1 else 2),
+            # per step: one kernel when the library balances the tiles itself (stage 1 merges, projects and,
+            # at N > 1, stores the rows to the peers in its last-arriving CTAs), else stage 1 + the merge
+            # kernel (+ the NCCL all-gather, which is not counted)
+            "gpu_launches": args.steps * (1 if m.balanced and (world == 1 or m.pg is not None) else 2),
             "kernel_status": int(status.item()),
             "clocks": clocks,
         }
@@ -679,7 +681,7 @@ def main():
             ok_x = mx.gather_check()
             if rank == 0:
                 strong.append({
-                    "workload": name, "heads_per_gpu": mx.H, "split_len": mx.split_len, "n_splits": mx.n_splits,
+                    "workload": name, "heads_per_gpu": mx.H, "distribution": mx.distribution,
                     "steps": k, "us_per_layer": ms_x * 1e3, "GB/s": mx.bytes_total / (ms_x * 1e-3) / 1e9,
                     "us_stage1": ms_x1 * 1e3, "stage1_frac_per_gpu": mx.bytes_rank / (ms_x1 * 1e-3) / 1e9 / peak,
                     "gather_check": ok_x})

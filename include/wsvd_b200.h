@@ -225,15 +225,16 @@ typedef struct WsvdQuantAppendParams {
 int wsvd_latent_quant_append_i8(const WsvdQuantAppendParams* p, void* stream);
 
 /*
- * Head-sharded multi-GPU decode with the all-gather fused into the merge kernel.
+ * Head-sharded multi-GPU decode with the all-gather fused into the op's own kernels.
  *
  * The op shards by attention head with no exchange between heads
  * (flash_int8_latent_per_head_decoding_rope_stage1.py:60, program_id(1) = head); the one
  * exchange of the path is the all-gather of the [B, H/g, D] outputs.  The reference is
- * single-GPU and has no counterpart.  Here every rank's merge kernel stores its rows
- * straight into the gathered [B, H_total, D] f16 buffer of EVERY rank (plain peer stores,
- * no multicast), and its last block runs the group barrier: a system-scope fence, one flag
- * store per peer and a bounded wait for the peers' flags.  When the call's kernels have
+ * single-GPU and has no counterpart.  Here the kernel that finishes an output row (the decode
+ * kernel itself when it balances the work over persistent CTAs, else the merge kernel) stores
+ * it straight into the gathered [B, H_total, D] f16 buffer of EVERY rank (plain 16-byte peer
+ * stores, no multicast), and its last block runs the group barrier: a system-scope fence, one
+ * flag store per peer and a bounded wait for the peers' flags.  When the call's kernels have
  * finished on every rank, every rank's buffer holds all heads.
  *
  *  - out[i], flags[i]: rank i's gathered buffer and flag array (WSVD_MAX_PEERS uint32,

@@ -306,15 +306,28 @@ static int decode_impl(const WsvdLatentDecodeParams* p, const WsvdPeerSet* peers
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   void* scratch_table = p->rope_table ? nullptr : ws + l.table_off;
   wsvd::PartialIndex where = {nullptr, 0, ns, sl};
-  wsvd::Stage1Work work = {0, nullptr, nullptr};
+  wsvd::Stage1Work work = {0, nullptr, nullptr, nullptr};
+  wsvd::PeerArgs pa;
   if (balanced_mode(p)) {
     st = balanced_ctas(p, &work.n_ctas);
     if (st != WSVD_OK) return st;
     where.n_ctas = work.n_ctas;
-    if (merge && !peers) {
+    if (merge) {
       // one kernel: the CTA that completes a head's last partial merges and writes the output row
+      // (into every rank's gathered buffer when there are peers, followed by the group's barrier)
       work.arrivals = reinterpret_cast<unsigned int*>(ws + l.arrivals_off);
-      return run_stage1(a, scratch_table, work, s);
+      if (peers) {
+        // 16-byte peer stores need aligned rows; anything else goes through the merge kernel
+        bool vec = peers->out_stride_b % 8 == 0 && peers->out_stride_h % 8 == 0;
+        for (int i = 0; i < peers->n_peers; ++i) vec = vec && aligned16(peers->out[i]);
+        if (vec) {
+          pa = wsvd::make_peer_args(*peers);
+          work.peers = &pa;
+        } else {
+          work.arrivals = nullptr;
+        }
+      }
+      if (work.arrivals) return run_stage1(a, scratch_table, work, s);
     }
     work.prefix = reinterpret_cast<int32_t*>(ws + l.prefix_off);
     where.prefix = work.prefix;
@@ -393,7 +406,7 @@ int wsvd_latent_decode_stage1(const WsvdLatentDecodeParams* p, float* mid_o, flo
   if ((long)n_splits * p->split_len < p->max_len) return WSVD_ERR_WORKSPACE_TOO_SMALL;
   wsvd::KArgs a;
   fill_args(p, mid_o, lse, p->split_len, n_splits, &a);
-  return run_stage1(a, nullptr, wsvd::Stage1Work{0, nullptr, nullptr}, reinterpret_cast<cudaStream_t>(stream));
+  return run_stage1(a, nullptr, wsvd::Stage1Work{0, nullptr, nullptr, nullptr}, reinterpret_cast<cudaStream_t>(stream));
 }
 
 static void dense_plan(const WsvdDenseDecodeParams* p, int* sl, int* ns) {

@@ -19,24 +19,7 @@ namespace {
 
 constexpr int kThreads = 128;
 constexpr int kMaxOutRow = 1024;  // widest output row (head_dim) the entry points accept
-constexpr unsigned int kPeerWaitTimedOut = 6;
 __device__ unsigned int g_peer_status = 0;
-
-struct PeerArgs {
-  __half* out[WSVD_MAX_PEERS];
-  uint32_t* flags[WSVD_MAX_PEERS];
-  uint32_t* counter;
-  uint32_t* epoch_counter;
-  int32_t n_peers, rank, head_offset;
-  uint32_t epoch;
-  uint64_t timeout_ns;
-};
-
-__device__ __forceinline__ uint64_t global_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
 
 template <bool kPeers>
 __global__ void __launch_bounds__(kThreads)
@@ -77,7 +60,8 @@ stage2_kernel(const float* __restrict__ mid_o, const float* __restrict__ lse, co
     for (int i = 0; i < ns; ++i) o = fmaf(__expf(lse[slot0 + i * step] - m), mid_o[(slot0 + i * step) * width + r], o);
     o /= wsum;
   }
-  const int64_t doff = (int64_t)b * out_stride_b + (int64_t)(h + (kPeers ? pa.head_offset : 0)) * out_stride_h;
+  const int64_t doff = kPeers ? (int64_t)b * pa.out_stride_b + (int64_t)(h + pa.head_offset) * pa.out_stride_h
+                              : (int64_t)b * out_stride_b + (int64_t)h * out_stride_h;
   // With peers the finished row is staged in shared memory and leaves as 16-byte stores, one per
   // thread per peer (a 128-dim row is 16 such stores per peer), instead of one 2-byte store per
   // element per peer: NVLink carries far fewer, fuller packets.
@@ -141,31 +125,7 @@ stage2_kernel(const float* __restrict__ mid_o, const float* __restrict__ lse, co
     __syncthreads();
     if (!last) return;
     if (threadIdx.x == 0) *pa.counter = 0u;  // ready for the next launch
-    // the step's epoch: the caller's, or one more than the device-side count of past steps
-    uint32_t epoch = pa.epoch;
-    if (pa.epoch_counter != nullptr) {
-      epoch = *reinterpret_cast<volatile uint32_t*>(pa.epoch_counter) + 1u;
-      __syncthreads();  // every thread of this (last) block has read the old count
-      if (threadIdx.x == 0) *pa.epoch_counter = epoch;
-    }
-    __threadfence_system();
-    const int i = threadIdx.x;
-    if (i < pa.n_peers) {
-      // "rank pa.rank has delivered epoch e" into peer i's flag array ...
-      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pa.flags[i] + pa.rank), "r"(epoch) : "memory");
-      // ... and wait for peer i's word in ours; epochs only grow (wrap-safe comparison)
-      const uint32_t* mine = pa.flags[pa.rank] + i;
-      const uint64_t t0 = global_ns();
-      for (;;) {
-        uint32_t v;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
-        if ((int32_t)(v - epoch) >= 0) break;
-        if (global_ns() - t0 > pa.timeout_ns) {
-          atomicMax(&g_peer_status, kPeerWaitTimedOut);
-          break;
-        }
-      }
-    }
+    peer_group_barrier(pa, &g_peer_status);
   }
 }
 
@@ -187,21 +147,9 @@ cudaError_t launch_stage2_peers(const float* mid_o, const float* lse, const int3
                                 const WsvdPeerSet& peers, int batch, int n_q_heads, const PartialIndex& where,
                                 int width, const void* wv, int64_t wv_stride_r, int n_kv_heads, int head_dim,
                                 cudaStream_t stream) {
-  PeerArgs pa{};
-  for (int i = 0; i < peers.n_peers; ++i) {
-    pa.out[i] = reinterpret_cast<__half*>(peers.out[i]);
-    pa.flags[i] = peers.flags[i];
-  }
-  pa.counter = peers.counter;
-  pa.epoch_counter = peers.epoch_counter;
-  pa.n_peers = peers.n_peers;
-  pa.rank = peers.rank;
-  pa.head_offset = peers.head_offset;
-  pa.epoch = peers.epoch;
-  pa.timeout_ns = peers.timeout_ms > 0 ? (uint64_t)peers.timeout_ms * 1000000ull : 2000000000ull;
+  const PeerArgs pa = make_peer_args(peers);
   dim3 grid(n_q_heads, batch);
-  stage2_kernel<true><<<grid, kThreads, 0, stream>>>(mid_o, lse, b_seq_len, nullptr, peers.out_stride_b,
-                                                     peers.out_stride_h, n_q_heads, where, width,
+  stage2_kernel<true><<<grid, kThreads, 0, stream>>>(mid_o, lse, b_seq_len, nullptr, 0, 0, n_q_heads, where, width,
                                                      reinterpret_cast<const __half*>(wv), wv_stride_r, n_kv_heads,
                                                      head_dim, pa);
   return cudaGetLastError();

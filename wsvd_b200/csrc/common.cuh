@@ -81,15 +81,87 @@ int record_cuda_error(cudaError_t e);
 
 // Launchers implemented in the kernel translation units.
 cudaError_t launch_stage1_generic(const KArgs& a, cudaStream_t stream);
+// A head-sharded group of GPUs: where every rank's gathered [B, H_total, D] buffer and flag array are
+// mapped, and the state of the group barrier (see combine.cu).
+struct PeerArgs {
+  __half* out[WSVD_MAX_PEERS];
+  uint32_t* flags[WSVD_MAX_PEERS];
+  uint32_t* counter;
+  uint32_t* epoch_counter;
+  int64_t out_stride_b, out_stride_h;
+  int32_t n_peers, rank, head_offset;
+  uint32_t epoch;
+  uint64_t timeout_ns;
+};
+constexpr unsigned int kPeerWaitTimedOut = 6;
+
+inline PeerArgs make_peer_args(const WsvdPeerSet& peers) {
+  PeerArgs pa{};
+  for (int i = 0; i < peers.n_peers; ++i) {
+    pa.out[i] = reinterpret_cast<__half*>(peers.out[i]);
+    pa.flags[i] = peers.flags[i];
+  }
+  pa.counter = peers.counter;
+  pa.epoch_counter = peers.epoch_counter;
+  pa.out_stride_b = peers.out_stride_b;
+  pa.out_stride_h = peers.out_stride_h;
+  pa.n_peers = peers.n_peers;
+  pa.rank = peers.rank;
+  pa.head_offset = peers.head_offset;
+  pa.epoch = peers.epoch;
+  pa.timeout_ns = peers.timeout_ms > 0 ? (uint64_t)peers.timeout_ms * 1000000ull : 2000000000ull;
+  return pa;
+}
+
+#ifdef __CUDACC__
+// The group's barrier, run by every thread of the block that finishes last (the caller has made
+// sure that every block's peer stores are fenced and counted): bump the step's epoch, tell every
+// peer "rank r has delivered epoch e" and wait, with a time limit, until every peer's word for this
+// rank shows the epoch.  On a time-out kPeerWaitTimedOut is recorded in *status.
+__device__ __forceinline__ void peer_group_barrier(const PeerArgs& pa, unsigned int* status) {
+  // the step's epoch: the caller's, or one more than the device-side count of past steps
+  uint32_t epoch = pa.epoch;
+  if (pa.epoch_counter != nullptr) {
+    epoch = *reinterpret_cast<volatile uint32_t*>(pa.epoch_counter) + 1u;
+    __syncthreads();  // every thread of this (last) block has read the old count
+    if (threadIdx.x == 0) *pa.epoch_counter = epoch;
+  }
+  __threadfence_system();
+  const int i = threadIdx.x;
+  if (i < pa.n_peers) {
+    // "rank pa.rank has delivered epoch e" into peer i's flag array ...
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pa.flags[i] + pa.rank), "r"(epoch) : "memory");
+    // ... and wait for peer i's word in ours; epochs only grow (wrap-safe comparison)
+    const uint32_t* mine = pa.flags[pa.rank] + i;
+    uint64_t t0;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+    for (;;) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+      if ((int32_t)(v - epoch) >= 0) break;
+      uint64_t now;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+      if (now - t0 > pa.timeout_ns) {
+        atomicMax(status, kPeerWaitTimedOut);
+        break;
+      }
+    }
+  }
+}
+#endif
+
 // How the tensor-core kernel distributes its work.  n_ctas == 0: one CTA per (split, head group,
 // sequence), partials in the split layout.  n_ctas > 0: that many persistent CTAs with equal shares
 // of the tile list, partials in the balanced layout; then either `prefix` ([batch + 2] int32, written
 // by the kernel for the merge kernel) or `arrivals` ([batch * n_q_heads] uint32, zeroed by the
-// launcher: the kernel merges, applies U_v and writes p.out itself) is given.
+// launcher: the kernel merges, applies U_v and writes the output rows itself) is given.  With
+// `arrivals` and `peers`, the rows go into every rank's gathered buffer instead of p.out and the CTA
+// that finishes last runs the group's barrier: the head all-gather is part of the kernel.
 struct Stage1Work {
   int n_ctas;
   int32_t* prefix;
   unsigned int* arrivals;
+  const PeerArgs* peers;
 };
 cudaError_t launch_stage1_tc(const KArgs& a, const void* table, int table_rows, const Stage1Work& work,
                              cudaStream_t stream);

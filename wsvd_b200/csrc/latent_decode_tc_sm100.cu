@@ -327,6 +327,8 @@ struct TcArgs {
   int32_t balanced;        // 0: split mode
   int32_t* prefix_out;     // balanced mode: [batch + 2] tile prefix sums and share count for the merge kernel, or null
   unsigned int* arrivals;  // balanced mode: [batch * n_q_heads] zeroed arrival counters = merge inside this kernel, or null
+  int32_t has_peers;       // with arrivals: output rows go to every rank's gathered buffer, group barrier at the end
+  PeerArgs peers;
   alignas(64) CUtensorMap tmap_k;      // latents as 3-D byte tensors: box 64 bytes x 64 slots x box_heads,
   alignas(64) CUtensorMap tmap_v;      // 64-byte swizzle
   alignas(64) CUtensorMap tmap_table;  // [2][rows][64] f16, box 64 x 128 x 2 (cos and sin tile), 128-byte swizzle
@@ -447,9 +449,18 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
       const int n_out = p.wv != nullptr ? p.head_dim : Rv;
       for (int bb = blockIdx.x; bb < p.batch; bb += gridDim.x) {
         if (p.b_seq_len[bb] > 0) continue;
-        __half* orow = reinterpret_cast<__half*>(p.out) + (int64_t)bb * p.out_stride_b;
-        for (int i = threadIdx.x; i < p.n_q_heads * n_out; i += kThreads)
-          orow[(int64_t)(i / n_out) * p.out_stride_h + i % n_out] = __float2half_rn(0.f);
+        if (ta.has_peers) {
+          for (int i = threadIdx.x; i < p.n_q_heads * n_out * ta.peers.n_peers; i += kThreads) {
+            const int peer = i / (p.n_q_heads * n_out), j = i % (p.n_q_heads * n_out);
+            ta.peers.out[peer][(int64_t)bb * ta.peers.out_stride_b +
+                               (int64_t)(j / n_out + ta.peers.head_offset) * ta.peers.out_stride_h + j % n_out] =
+                __float2half_rn(0.f);
+          }
+        } else {
+          __half* orow = reinterpret_cast<__half*>(p.out) + (int64_t)bb * p.out_stride_b;
+          for (int i = threadIdx.x; i < p.n_q_heads * n_out; i += kThreads)
+            orow[(int64_t)(i / n_out) * p.out_stride_h + i % n_out] = __float2half_rn(0.f);
+        }
       }
     }
   } else {
@@ -1060,7 +1071,11 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
       }
       if (finish) {
         asm volatile("bar.sync %0, %1;" ::"r"(1 + g), "r"(128) : "memory");
-        __half* out = reinterpret_cast<__half*>(p.out) + (int64_t)b * p.out_stride_b + (int64_t)h * p.out_stride_h;
+        // with peers the finished row is staged (second half of the head's plane area) and leaves as
+        // 16-byte stores, one per thread per peer
+        __half* stage = reinterpret_cast<__half*>(sm + kOffPlanes + 2 * g * kPlaneBytes + kPlaneBytes);
+        __half* out = ta.has_peers ? stage
+                                   : reinterpret_cast<__half*>(p.out) + (int64_t)b * p.out_stride_b + (int64_t)h * p.out_stride_h;
         const int d = q4 * 32 + lane;
         if (p.wv == nullptr) {
           if (d < Rv) out[d] = __float2half_rn(o_row[d]);
@@ -1076,6 +1091,15 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
             y3 = fmaf(o_row[k + 3], __half2float(__ldg(w + (int64_t)(k + 3) * p.wv_stride_r)), y3);
           }
           out[d] = __float2half_rn((y0 + y1) + (y2 + y3));
+        }
+        if (ta.has_peers) {
+          asm volatile("bar.sync %0, %1;" ::"r"(1 + g), "r"(128) : "memory");
+          const int chunks = (p.wv == nullptr ? Rv : p.head_dim) >> 3;
+          const int64_t doff = (int64_t)b * ta.peers.out_stride_b + (int64_t)(h + ta.peers.head_offset) * ta.peers.out_stride_h;
+          for (int idx = d; idx < chunks * ta.peers.n_peers; idx += 128) {
+            const int peer = idx / chunks, c = idx - peer * chunks;
+            *reinterpret_cast<uint4*>(ta.peers.out[peer] + doff + 8 * c) = reinterpret_cast<const uint4*>(stage)[c];
+          }
         }
       }
     }
@@ -1133,10 +1157,22 @@ __global__ void __launch_bounds__(kThreads, 1) stage1_tc_kernel(const __grid_con
 
   // ---- common exit
   tc_fence_before();
+  if (ta.has_peers) __threadfence_system();  // this thread's peer stores are ordered before the count below
   __syncthreads();
   if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(*tmem_slot, kTmemCols);
+  }
+  if (ta.has_peers) {
+    // the group's barrier, run by whichever CTA finishes last
+    volatile int* last = reinterpret_cast<volatile int*>(sm + kOffSum);
+    if (threadIdx.x == 0) {
+      const unsigned int done = atomicAdd(ta.peers.counter, 1u) + 1u;
+      *last = done == gridDim.x;
+      if (done == gridDim.x) *ta.peers.counter = 0u;  // ready for the next launch
+    }
+    __syncthreads();
+    if (*last) peer_group_barrier(ta.peers, &g_status);
   }
 }
 
@@ -1240,6 +1276,9 @@ cudaError_t launch_stage1_tc(const KArgs& a, const void* table, int table_rows, 
   ta.balanced = work.n_ctas > 0;
   ta.prefix_out = work.prefix;
   ta.arrivals = work.arrivals;
+  ta.has_peers = work.arrivals != nullptr && work.peers != nullptr;
+  if (ta.has_peers) ta.peers = *work.peers;
+  else memset(&ta.peers, 0, sizeof(ta.peers));
   const int grid = work.n_ctas > 0 ? work.n_ctas : a.n_splits * ((a.p.n_q_heads + tc::kG - 1) / tc::kG) * a.p.batch;
   if (work.n_ctas > 0 && work.arrivals != nullptr) {
     e = cudaMemsetAsync(work.arrivals, 0, sizeof(unsigned int) * (size_t)a.p.batch * a.p.n_q_heads, stream);

@@ -55,11 +55,11 @@ class _DeviceArray:
 
 
 class PeerGather:
-    """Head-sharded decode whose all-gather is fused into the merge kernel.
+    """Head-sharded decode whose all-gather is fused into the op's own kernels.
 
     Every rank owns two gathered output buffers [B, H_total, D] f16 (used alternately, by step
     parity), a flag array and a block counter in memory that the other ranks map through
-    CUDA IPC.  `decode(...)` runs this rank's shard; its merge kernel stores the rows into
+    CUDA IPC.  `decode(...)` runs this rank's shard; the kernel that finishes a row stores it into
     all ranks' buffers over NVLink and runs the group barrier in its last block, so when
     the returned tensor is read on the same stream it holds every rank's heads.  No NCCL
     call is made per step; torch.distributed is used once, to exchange the handles.
