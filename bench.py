@@ -216,7 +216,10 @@ def run_c5(args):
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
         collective = "nccl all_gather of [B,H_local,128] f16 per layer; nccl all_reduce of the FFN output"
-        if args.collective == "fused":
+        if args.o_proj == "row":
+            collective = ("row-parallel o-projection: nccl all_reduce of [B,hidden] f16 per layer instead of a head "
+                          "gather; nccl all_reduce of the FFN output")
+        elif args.collective == "fused":
             from wsvd_b200.dist import PeerGather
             ok = torch.ones(1, device=dev)
             try:
@@ -231,7 +234,8 @@ def run_c5(args):
             else:
                 collective = ("head all-gather fused into the decode kernel (peer stores + flag barrier) per layer; "
                               "nccl all_reduce of the FFN output")
-    model = LatentDecoder(spec, B, context, capacity, rank=rank, world=world, device=dev, seed=5, peer_gather=pg)
+    model = LatentDecoder(spec, B, context, capacity, rank=rank, world=world, device=dev, seed=5, peer_gather=pg,
+                          o_proj=args.o_proj, fused_elementwise=not args.torch_elementwise)
     x = (torch.randn(B, spec.hidden, device=dev, dtype=torch.float32) * 0.5).to(torch.float16)
 
     def barrier():
@@ -242,7 +246,7 @@ def run_c5(args):
     graph = None
     # (with the NCCL head gather the step is launched from Python: a run that captured it in a graph
     # did not finish and was not repeated)
-    if not args.no_graph and (world == 1 or pg is not None):
+    if not args.no_graph and (world == 1 or pg is not None or args.o_proj == "row"):
         graph, y_graph = model.capture(x)  # one CUDA graph replayed per step (advances the context by one)
 
     def step():
@@ -317,6 +321,8 @@ def run_c5(args):
                        "hidden": spec.hidden, "heads": spec.heads, "heads_per_gpu": spec.heads // world,
                        "ffn": spec.ffn, "rank_k": spec.rank_k, "rank_v": spec.rank_v,
                        "parallelism": f"heads x{world}", "collective": collective,
+                       "o_proj": model.o_proj,
+                       "elementwise": "torch chains" if args.torch_elementwise else "one kernel each",
                        "launch": "one CUDA graph per step" if graph is not None else "eager, from Python",
                        "l2": "caches and weights of one step (GBs per GPU) are larger than the 126 MB L2"},
             "roofline": {"bound": "hbm", "kernel": "whole step: latent+scale bytes of 32 layers + the rank's weights",
@@ -325,20 +331,21 @@ def run_c5(args):
                          "attention_bytes_per_step": model.attention_bytes(), "traffic": None},
             "e2e": {"value": B / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
-            "gpu_launches": steps * spec.layers * 3,
+            # this package's kernels per layer: quantise-and-append, decode (+ RMSNorm x2, RoPE, SiLU*up)
+            "gpu_launches": steps * spec.layers * (2 + (0 if args.torch_elementwise else 4)),
             "kernel_status": int(status.item()), "clocks": clocks,
         }), flush=True)
     if world > 1:
+        # The step's graph holds the captured NCCL all-reduces and the addresses of the peer buffers:
+        # it has to go before the buffers are unmapped and the communicator is destroyed (tearing
+        # those down under a live graph is what did not return on 8 ranks).
         if graph is not None:
-            # Every rank has passed the all-reduce of the status word after its last kernel.  With the
-            # NCCL all-reduce captured in the step's graph, tearing the peer buffers and the process
-            # group down did not return on 8 ranks; leave it to process exit.
-            sys.stdout.flush()
-            sys.stderr.flush()
-            os._exit(0)
+            graph.reset()
+            graph = None
+        torch.cuda.synchronize()
+        dist.barrier()
         if pg is not None:
             pg.close()
-        dist.barrier()
         dist.destroy_process_group()
 
 
@@ -575,6 +582,10 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="c5 step: launch from Python instead of one CUDA graph")
     ap.add_argument("--collective", default="fused", choices=["fused", "nccl"],
                     help="N>1: head all-gather fused into the decode kernel (peer stores), or an NCCL all_gather")
+    ap.add_argument("--o-proj", default="gather", choices=["gather", "row"],
+                    help="c5, N>1: heads gathered and a replicated Wo, or row-parallel Wo with an all-reduce")
+    ap.add_argument("--torch-elementwise", action="store_true",
+                    help="c5: RMSNorm / RoPE / SiLU*up as chains of torch ops instead of one kernel each")
     ap.add_argument("--no-dense", action="store_true", help="skip the dense f16 baseline kernel timing")
     ap.add_argument("--no-extra", action="store_true",
                     help="skip the `strong` list (c3, c4 at this N) and the reference Triton kernels")

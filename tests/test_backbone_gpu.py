@@ -79,3 +79,40 @@ def test_captured_step_replays_like_the_eager_one():
     assert ops.kernel_status() == 0
     assert torch.equal(y, want)
     assert int(graphed.after.b_seq_len[0]) == int(eager.after.b_seq_len[0]) + 1  # eager has not advanced yet
+
+
+def test_elementwise_kernels_match_the_torch_chains():
+    """RMSNorm, RoPE and SiLU*up as single kernels against the chains of torch ops they replace."""
+    from wsvd_b200 import ops
+    from wsvd_b200.backbone import _rms_norm, rope_half
+
+    g = torch.Generator(device="cuda").manual_seed(7)
+    x = (torch.randn(5, 4096, generator=g, device="cuda") * 0.7).to(torch.float16)
+    got, want = ops.rms_norm(x), _rms_norm(x)
+    assert (got.float() - want.float()).abs().max().item() <= 2e-3  # one f16 ulp near 2: the row sums differ in order
+
+    q = (torch.randn(5, 6, 128, generator=g, device="cuda")).to(torch.float16)
+    pos = torch.tensor([0, 1, 77, 4095, 31999], dtype=torch.int32, device="cuda")
+    inv = 10000.0 ** (-torch.arange(0, 128, 2, device="cuda", dtype=torch.float32) / 128)
+    want = rope_half(q, pos, 10000.0)
+    got = ops.rope_half_(q.clone(), pos, inv)
+    assert (got.float() - want.float()).abs().max().item() <= 4e-3  # f16 rounding of values up to ~4
+
+    up = (torch.randn(3, 11008, generator=g, device="cuda") * 2).to(torch.float16)
+    gate = (torch.randn(3, 11008, generator=g, device="cuda") * 2).to(torch.float16)
+    want = up * torch.nn.functional.silu(gate)
+    got = ops.silu_mul(up, gate)
+    assert (got.float() - want.float()).abs().max().item() <= 8e-3  # one f16 ulp at the largest products (~8..16)
+    torch.cuda.synchronize()
+
+
+def test_step_with_torch_elementwise_chains_agrees():
+    """The fused element-wise kernels change nothing beyond f16 rounding."""
+    from wsvd_b200.backbone import BackboneSpec, LatentDecoder
+
+    spec = BackboneSpec(layers=2, hidden=512, heads=4, head_dim=128, ffn=1024, rank_k=64, rank_v=64)
+    x = (torch.randn(3, 512, generator=torch.Generator().manual_seed(2)) * 0.5).to(torch.float16).cuda()
+    a = LatentDecoder(spec, batch=3, context=300, capacity=310, device="cuda", seed=1).step(x)
+    b = LatentDecoder(spec, batch=3, context=300, capacity=310, device="cuda", seed=1, fused_elementwise=False).step(x)
+    torch.cuda.synchronize()
+    assert (a.float() - b.float()).abs().max().item() <= 2e-2 * b.float().abs().max().item()

@@ -9,10 +9,12 @@ fake_quant/svd_utils.py:1628-1674, with the latent cache of the efficiency path)
     cache <- int8(xk), int8(xv)             quantise-and-append (wsvd_latent_quant_append_i8)
     o  = latent decode attention over len+1 tokens, U_v applied   (the op of this package)
     x  = x + gather_heads(o) @ Wo           heads gathered across ranks, then the o-projection
+                                            (o_proj="row": x + all_reduce(o_local @ Wo[rows of the shard]))
     x  = x + SwiGLU FFN(RMSNorm(x))         FFN sharded by columns/rows, all-reduced
 
 Random-init weights and caches; dense projections are torch matmuls (cuBLAS), everything
-on the attention path is this package's CUDA.  Rank r of g owns heads [r*H/g, (r+1)*H/g),
+on the attention path and the element-wise chains (RMSNorm, RoPE, SiLU*up: one kernel each,
+`fused_elementwise=False` runs them as the torch chains below instead) are this package's CUDA.  Rank r of g owns heads [r*H/g, (r+1)*H/g),
 their A_k/A_v/U_k/U_v/Wq columns and their cache shard.
 """
 from __future__ import annotations
@@ -63,8 +65,14 @@ class LatentDecoder:
     """Weights, latent caches and the decode step for this rank's shard."""
 
     def __init__(self, spec: BackboneSpec, batch: int, context: int, capacity: int, rank: int = 0, world: int = 1,
-                 device="cuda", seed: int = 0, peer_gather=None, group=None):
+                 device="cuda", seed: int = 0, peer_gather=None, group=None, o_proj: str = "gather",
+                 fused_elementwise: bool = True):
         assert spec.heads % world == 0 and spec.ffn % world == 0
+        assert o_proj in ("gather", "row")
+        # "gather": all ranks hold Wo and apply it to the gathered heads; "row": every rank applies its
+        # heads' rows of Wo to its own heads and the partial products are all-reduced
+        self.o_proj = o_proj if world > 1 else "gather"
+        self.fused_elementwise = fused_elementwise
         self.spec, self.batch, self.rank, self.world = spec, batch, rank, world
         self.device = torch.device(device)
         self.group, self.pg = group, peer_gather
@@ -92,6 +100,8 @@ class LatentDecoder:
             L.A_v = gauss(spec.hidden, Hl * spec.rank_v, s)
             L.wk, L.wv = ortho(spec.rank_k), ortho(spec.rank_v)
             L.Wo = gauss(spec.heads * spec.head_dim, spec.hidden, s)  # replicated: applied to the gathered heads
+            if self.o_proj == "row":  # keep only this rank's rows
+                L.Wo = L.Wo[rank * Hl * spec.head_dim:(rank + 1) * Hl * spec.head_dim].contiguous()
             L.Wup = gauss(spec.hidden, spec.ffn // world, s)
             L.Wgate = gauss(spec.hidden, spec.ffn // world, s)
             L.Wdown = gauss(spec.ffn // world, spec.hidden, 1.0 / math.sqrt(spec.ffn))
@@ -118,8 +128,10 @@ class LatentDecoder:
         self.context, self.capacity = context, capacity
         self.out_local = torch.empty(batch, Hl, spec.head_dim, dtype=dt, device=dev)
         self.gathered = (torch.empty(world, batch, Hl, spec.head_dim, dtype=dt, device=dev)
-                         if world > 1 and peer_gather is None else None)
+                         if world > 1 and peer_gather is None and self.o_proj == "gather" else None)
         self.workspace = None
+        self.inv_freq = spec.theta ** (-torch.arange(0, spec.head_dim, 2, device=dev, dtype=torch.float32)
+                                       / spec.head_dim)
 
     def attention_bytes(self) -> int:
         """Algorithmic latent+scale bytes one step reads on this rank (all layers)."""
@@ -135,6 +147,10 @@ class LatentDecoder:
 
     def _attend(self, L, q):
         sp = self.spec
+        if self.o_proj == "row":
+            o = ops.latent_decode(q, self.after, L.lk, L.ks, L.lv, L.vs, L.wk, None, wv=L.wv, out=self.out_local,
+                                  workspace=self.workspace)
+            return o.reshape(self.batch, self.local_heads * sp.head_dim)
         if self.pg is not None:
             full = self.pg.decode(q, self.after, L.lk, L.ks, L.lv, L.vs, L.wk, None, wv=L.wv,
                                   workspace=self.workspace)
@@ -162,19 +178,27 @@ class LatentDecoder:
                                     L0.vs, L0.wk, None, wv=L0.wv)
             self.workspace = torch.empty((ops.workspace_bytes(p) + 3) // 4, dtype=torch.float32, device=self.device)
         pos = self.before.b_seq_len
+        fe = self.fused_elementwise
+        if self.world > 1:
+            import torch.distributed as dist
         for L in self.layers:
-            xn = _rms_norm(x)
-            q = rope_half((xn @ L.Wq).view(B, Hl, sp.head_dim), pos, sp.theta)
+            xn = ops.rms_norm(x) if fe else _rms_norm(x)
+            q = (xn @ L.Wq).view(B, Hl, sp.head_dim)
+            q = ops.rope_half_(q, pos, self.inv_freq) if fe else rope_half(q, pos, sp.theta)
             xk = (xn @ L.A_k).view(B, Hl, sp.rank_k)
             xv = (xn @ L.A_v).view(B, Hl, sp.rank_v)
             ops.latent_quant_append(xk, xv, self.before, L.lk, L.ks, L.lv, L.vs)
             o = self._attend(L, q)
-            x = x + o @ L.Wo
-            h = _rms_norm(x)
-            f = ((h @ L.Wup) * torch.nn.functional.silu(h @ L.Wgate)) @ L.Wdown
+            if self.o_proj == "row":
+                a = o @ L.Wo
+                dist.all_reduce(a, group=self.group)
+                x = x + a
+            else:
+                x = x + o @ L.Wo
+            h = ops.rms_norm(x) if fe else _rms_norm(x)
+            up, gate = h @ L.Wup, h @ L.Wgate
+            f = (ops.silu_mul(up, gate) if fe else up * torch.nn.functional.silu(gate)) @ L.Wdown
             if self.world > 1:
-                import torch.distributed as dist
-
                 dist.all_reduce(f, group=self.group)
             x = x + f
         return x
@@ -185,7 +209,7 @@ class LatentDecoder:
         the head gather has to be the fused one with its epoch on the device
         (`PeerGather(device_epoch=True)`); the FFN's NCCL all-reduce is captured as it is.  Returns (graph, output tensor); replay
         with graph.replay() after writing the new input into x."""
-        assert (self.world == 1 and self.pg is None) or (self.pg is not None and self.pg.device_epoch)
+        assert self.world == 1 or self.o_proj == "row" or (self.pg is not None and self.pg.device_epoch)
         self.before.max_len_in_batch = self.capacity
         self.after.max_len_in_batch = self.capacity
         side = torch.cuda.Stream(device=self.device)

@@ -1,0 +1,95 @@
+// Element-wise kernels of the decode step around the attention op: RMSNorm, rotary embedding of
+// the new query, SiLU(gate) * up.  In the accuracy pipeline these are chains of small torch ops
+// (fake_quant/svd_utils.py:1628-1674: LlamaRMSNorm, apply_rotary_pos_emb, the MLP's act_fn); a
+// decode step of batch 64 spends a third of its time launching them, so each chain is one kernel
+// here.  f16 in and out, fp32 arithmetic, rounding at the same places as the torch chains.
+#include "common.cuh"
+
+namespace wsvd {
+namespace {
+
+// y[r, :] = f16( x[r, :] * rsqrt(mean(x[r, :]^2) + eps) ), one block per row
+__global__ void __launch_bounds__(256) rms_norm_kernel(const __half* __restrict__ x, __half* __restrict__ y, int cols,
+                                                       float eps) {
+  const __half* xr = x + (int64_t)blockIdx.x * cols;
+  __half* yr = y + (int64_t)blockIdx.x * cols;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < cols; i += 256) {
+    const float v = __half2float(xr[i]);
+    ss = fmaf(v, v, ss);
+  }
+  ss = warp_sum(ss);
+  __shared__ float part[8];
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) tot += part[w];
+  const float scale = rsqrtf(tot / (float)cols + eps);
+  for (int i = threadIdx.x; i < cols; i += 256) yr[i] = __float2half_rn(__half2float(xr[i]) * scale);
+}
+
+// half-split rotary embedding in place: q[b, h, i], q[b, h, i + D/2] rotated by pos[b] * inv_freq[i]
+__global__ void rope_half_kernel(__half* __restrict__ q, const int32_t* __restrict__ pos,
+                                 const float* __restrict__ inv_freq, int heads, int half_dim, int64_t total) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int i = (int)(idx % half_dim);
+  const int64_t bh = idx / half_dim;
+  const int b = (int)(bh / heads);
+  float sn, cs;
+  sincosf((float)pos[b] * inv_freq[i], &sn, &cs);
+  __half* row = q + bh * (2 * half_dim);
+  const float lo = __half2float(row[i]), hi = __half2float(row[i + half_dim]);
+  row[i] = __float2half_rn(lo * cs - hi * sn);
+  row[i + half_dim] = __float2half_rn(hi * cs + lo * sn);
+}
+
+// out = up * f16(silu(gate)), the product rounded to f16 (the two roundings of the torch chain)
+__global__ void silu_mul_kernel(const __half* __restrict__ up, const __half* __restrict__ gate, __half* __restrict__ out,
+                                int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float g = __half2float(gate[i]);
+  const __half s = __float2half_rn(g / (1.f + expf(-g)));
+  out[i] = __float2half_rn(__half2float(up[i]) * __half2float(s));
+}
+
+}  // namespace
+}  // namespace wsvd
+
+extern "C" {
+
+int wsvd_rms_norm_f16(const void* x, void* y, int32_t rows, int32_t cols, float eps, void* stream) {
+  if (!x || !y) return WSVD_ERR_NULL_POINTER;
+  if (rows < 0 || cols <= 0) return WSVD_ERR_BAD_SHAPE;
+  if (rows == 0) return WSVD_OK;
+  wsvd::rms_norm_kernel<<<rows, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __half*>(x), reinterpret_cast<__half*>(y), cols, eps);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? WSVD_OK : wsvd::record_cuda_error(e);
+}
+
+int wsvd_rope_half_f16(void* q, const int32_t* pos, const float* inv_freq, int32_t batch, int32_t heads,
+                       int32_t head_dim, void* stream) {
+  if (!q || !pos || !inv_freq) return WSVD_ERR_NULL_POINTER;
+  if (batch < 0 || heads <= 0 || head_dim <= 0 || head_dim % 2) return WSVD_ERR_BAD_SHAPE;
+  const int64_t total = (int64_t)batch * heads * (head_dim / 2);
+  if (total == 0) return WSVD_OK;
+  wsvd::rope_half_kernel<<<(unsigned)((total + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<__half*>(q), pos, inv_freq, heads, head_dim / 2, total);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? WSVD_OK : wsvd::record_cuda_error(e);
+}
+
+int wsvd_silu_mul_f16(const void* up, const void* gate, void* out, int64_t n, void* stream) {
+  if (!up || !gate || !out) return WSVD_ERR_NULL_POINTER;
+  if (n < 0) return WSVD_ERR_BAD_SHAPE;
+  if (n == 0) return WSVD_OK;
+  wsvd::silu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __half*>(up), reinterpret_cast<const __half*>(gate), reinterpret_cast<__half*>(out), n);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? WSVD_OK : wsvd::record_cuda_error(e);
+}
+
+}  // extern "C"

@@ -430,3 +430,41 @@ def latent_quant_append(x_k, x_v, infer_state, cache_latent_k, cache_latent_k_sc
     p.x_dtype = 1 if x_k.dtype == torch.float16 else 2
     with torch.cuda.device(x_k.device):
         check(_lib.lib().wsvd_latent_quant_append_i8(ctypes.byref(p), _stream(stream)), "wsvd_latent_quant_append_i8")
+
+
+# ---- element-wise pieces of the decode step (one kernel each)
+
+def rms_norm(x: torch.Tensor, eps: float = 1e-5, out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+    """x [rows, cols] f16 -> x * rsqrt(mean(x^2) + eps), f16 (no weight vector)."""
+    _cuda_tensor("x", x, (torch.float16,), 2)
+    _need(x.is_contiguous(), "x must be contiguous")
+    if out is None:
+        out = torch.empty_like(x)
+    check(_lib.lib().wsvd_rms_norm_f16(_ptr(x), _ptr(out), x.shape[0], x.shape[1], float(eps), _stream(stream)),
+          "wsvd_rms_norm_f16")
+    return out
+
+
+def rope_half_(q: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor, stream=None) -> torch.Tensor:
+    """Half-split rotary embedding of q [B, H, D] f16 in place at positions pos [B] int32;
+    inv_freq [D/2] f32 on the device."""
+    _cuda_tensor("q", q, (torch.float16,), 3)
+    _cuda_tensor("pos", pos, (torch.int32,), 1)
+    _cuda_tensor("inv_freq", inv_freq, (torch.float32,), 1)
+    _need(q.is_contiguous() and pos.numel() == q.shape[0] and inv_freq.numel() * 2 == q.shape[2],
+          "q must be contiguous [B, H, D] with B positions and D/2 frequencies")
+    check(_lib.lib().wsvd_rope_half_f16(_ptr(q), _ptr(pos), _ptr(inv_freq), q.shape[0], q.shape[1], q.shape[2],
+                                        _stream(stream)), "wsvd_rope_half_f16")
+    return q
+
+
+def silu_mul(up: torch.Tensor, gate: torch.Tensor, out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+    """up * silu(gate), f16, same shape."""
+    _cuda_tensor("up", up, (torch.float16,), up.dim())
+    _cuda_tensor("gate", gate, (torch.float16,), up.dim())
+    _need(up.shape == gate.shape and up.is_contiguous() and gate.is_contiguous(), "up and gate: same contiguous shape")
+    if out is None:
+        out = torch.empty_like(up)
+    check(_lib.lib().wsvd_silu_mul_f16(_ptr(up), _ptr(gate), _ptr(out), up.numel(), _stream(stream)),
+          "wsvd_silu_mul_f16")
+    return out
