@@ -46,7 +46,10 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one stage-1 launch from an ncu capture, keyed by
 # workload: (bytes, sha256[:12] of the stage-1 kernel source the capture was taken with).  The
 # number is reported only while the kernel source is unchanged; otherwise `traffic` is null.
-NCU_TRAFFIC = {}
+NCU_TRAFFIC = {
+    "c2_13b_b16_s8192": (703951104, "dd5d0e2f27ce"),
+    "c4_13b_b64_ragged32k": (5328497808, "dd5d0e2f27ce"),
+}
 STAGE1_SOURCE = os.path.join(ROOT, "wsvd_b200", "csrc", "latent_decode_tc_sm100.cu")
 
 
