@@ -108,7 +108,9 @@ int wsvd_rope_table_init(void* table, size_t table_bytes, int32_t positions, int
  * 3 epilogue), 4 its shared-memory base was misaligned, 5 wsvd_latent_quant_append_i8 met
  * a position outside [0, max_len) and skipped that row, 6 the group barrier of
  * wsvd_latent_decode_gather gave up waiting for a peer.  SYNCHRONISES the device; meant
- * for tests and diagnostics.  wsvd_kernel_status_reset clears it.
+ * for tests and diagnostics, and for a serving loop to poll at a point where it synchronises
+ * anyway.  wsvd_kernel_status_reset clears it.  A tensor-core work item whose wait timed out
+ * writes NaN instead of its result, so the affected output rows are NaN, not plausible numbers.
  */
 int wsvd_kernel_status(uint32_t* status);
 int wsvd_kernel_status_reset(void);
@@ -259,7 +261,8 @@ int wsvd_silu_mul_f16(const void* up, const void* gate, void* out, int64_t n, vo
  *    epoch_counter is set the kernel takes *epoch_counter + 1 instead and stores it back, so
  *    that nothing in the argument block changes from step to step and the call can sit in a
  *    captured CUDA graph; `epoch` is then ignored.
- *  - Every rank must make the call with the same batch; p->out is ignored; p->n_q_heads is
+ *  - Every rank must make the call with the same batch, which must not be 0 (a rank that launched
+ *    nothing would leave its peers waiting: WSVD_ERR_BAD_SHAPE); p->out is ignored; p->n_q_heads is
  *    the LOCAL head count and head_offset the first global head of the shard.
  *  - Reuse: a rank may overwrite a peer's buffer for step e+1 while that peer still reads
  *    step e.  Alternate between two buffers by epoch parity and consume a buffer on the

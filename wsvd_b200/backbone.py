@@ -176,7 +176,13 @@ class LatentDecoder:
             p, _ = ops.build_params(q0, self.after.b_seq_len, self.after.b_req_idx,
                                     self.after.req_manager.req_to_token_indexs, self.capacity, L0.lk, L0.ks, L0.lv,
                                     L0.vs, L0.wk, None, wv=L0.wv)
-            self.workspace = torch.empty((ops.workspace_bytes(p) + 3) // 4, dtype=torch.float32, device=self.device)
+            # the split plan (where one is used) depends on max_len: take the largest request over the
+            # lengths this decoder can run at
+            need = 0
+            for max_len in sorted({self.capacity, *range(max(1, self.context), self.capacity + 1, 128)}):
+                p.max_len = max_len
+                need = max(need, ops.workspace_bytes(p))
+            self.workspace = torch.empty((need + 3) // 4, dtype=torch.float32, device=self.device)
         pos = self.before.b_seq_len
         fe = self.fused_elementwise
         if self.world > 1:

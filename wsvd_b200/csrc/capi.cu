@@ -362,6 +362,8 @@ int wsvd_latent_decode_gather(const WsvdLatentDecodeParams* p, const WsvdPeerSet
   if (!peers->counter) return WSVD_ERR_NULL_POINTER;
   for (int i = 0; i < peers->n_peers; ++i)
     if (!peers->out[i] || !peers->flags[i]) return WSVD_ERR_NULL_POINTER;
+  // a rank without sequences would launch nothing and leave its peers waiting at the group barrier
+  if (p && p->batch == 0) return WSVD_ERR_BAD_SHAPE;
   return decode_impl(p, peers, workspace, workspace_bytes, stream);
 }
 

@@ -1029,7 +1029,9 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
                                   : ((int64_t)b * p.n_q_heads + h) * a.n_splits + split;
     const int r = 16 * q4 + lane;
     // sum_s 2^z sv Lv / sum_s 2^z  =  acc * 2^(big_m - m_all) / l
-    const float o = big_m > -INFINITY ? acc * fast_exp2(big_m - m_all) / l_tot : 0.f;
+    // (after a wait that timed out the item's result is poisoned: NaN here propagates through the
+    // merge into the output row, so a time-out cannot pass for a valid result)
+    const float o = !ok ? __int_as_float(0x7fc00000) : big_m > -INFINITY ? acc * fast_exp2(big_m - m_all) / l_tot : 0.f;
     const bool alone = fused && n_parts == 1;  // this CTA covered the whole (sequence, head): no partials
     if (!alone) {
       if (lane < 16 && r < Rv) a.mid_o[slot * Rv + r] = o;
