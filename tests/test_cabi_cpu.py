@@ -186,6 +186,15 @@ def test_gather_needs_every_peer_pointer():
     assert lib.wsvd_latent_decode_gather(ctypes.byref(_params()), None, ctypes.c_void_p(0x2000), 1 << 30, None) == 1
 
 
+def test_gather_rejects_an_empty_batch():
+    """A rank that launched nothing would leave its peers waiting at the group barrier."""
+    lib = _lib.lib()
+    p = _params()
+    p.batch = 0
+    assert lib.wsvd_latent_decode_gather(ctypes.byref(p), ctypes.byref(_peer_set()), ctypes.c_void_p(0x2000), 1 << 30,
+                                         None) == 2
+
+
 def test_python_ops_refuse_cpu_tensors():
     """There is no CPU path: the ops raise before anything is launched."""
     import torch

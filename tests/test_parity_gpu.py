@@ -69,6 +69,17 @@ def test_token_major_layout_and_shuffled_page_table(kernel, shuffle):
 
 
 @pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("page_size", [128, 64, 256])
+def test_paged_cache_with_shuffled_pages(kernel, page_size):
+    """Pages of consecutive token slots in shuffled order: tiles that lie inside one page are fetched
+    with tensor copies, tiles that straddle pages (page size 64, ragged starts) by the gather."""
+    base = inputs.make_case(3, 8, 128, 64, 48, [1025, 300, 1792], 1792, seed=13)
+    case = inputs.token_major_copy(base, shuffle_seed=9, page_size=page_size)
+    assert_close(run_i8(case, kernel), oracle_for(base), f"paged page_size={page_size}")
+    assert_close(run_i8(case, kernel, split_len=256), oracle_for(base), f"paged page_size={page_size}, split 256")
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
 def test_determinism_bitwise(kernel):
     case = inputs.make_case(2, 4, 128, 64, 64, [900, 2000], 2000, seed=3).to("cuda")
     s = case.infer_state

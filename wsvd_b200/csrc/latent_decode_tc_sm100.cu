@@ -497,14 +497,9 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
 
   const int32_t* page = p.req_to_token + (int64_t)p.b_req_idx[b] * p.rtt_stride;
 
-  int run_breaks = 0;
-#pragma unroll 4
-  for (int i = threadIdx.x; i + 1 < hi - lo; i += kThreads) run_breaks |= page[lo + i + 1] - page[lo + i] - 1;
-
   uint4 wpre[8], qpre[2];
   // requested during set-up so that their latency is hidden behind it
-  int slot_n = -1, slot_lo = 0;
-  bool affine = false;
+  int slot_n = -1;
   unsigned short sk_raw = 0, sv_raw = 0;
 
   // ---- set-up of the item: barriers (MMA warp), first loads (the others)
@@ -522,8 +517,6 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
       mbar_init(bar(i), count);
     }
     fence_barrier_init();
-  } else {
-    slot_lo = page[lo];
   }
   } else {
   if (warp < 4 * G) {
@@ -565,10 +558,7 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
     }
   }
   }
-  // Tensor copies need the split's token slots to be one run of consecutive slots (true for a cache
-  // laid out sequence by sequence).  Every thread compares a few neighbouring page entries (all
-  // loads independent, issued at the top of the kernel) and the barrier combines the verdicts.
-  affine = __syncthreads_and(run_breaks == 0) != 0 && ta.use_tma != 0;
+  __syncthreads();
   tc_fence_after();
   tmem = *tmem_slot;
 
@@ -623,19 +613,43 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
     const bool is_loader = pw == 0;
     const int hk0 = h0 / gqa, nkv = (h0 + G - 1) / gqa - hk0 + 1;  // the group's KV heads
     bool ok = true;
+    // A tensor copy needs the tile's token slots to be one run of consecutive slots (true for a cache
+    // laid out sequence by sequence, and for every tile inside a page of a paged cache).  The
+    // requesting warp checks that tile by tile: lane l holds the page entries of tokens 4l..4l+3 of
+    // the tile it will request next (fetched one tile ahead), and the warp votes.  `run_first`: the
+    // slot of the tile's first token.
+    int ent[4];
+    int run_tile = -1, run_first = 0;
+    bool run_ok = false;
+    auto fetch_entries = [&](int nu) {
+      const int s0 = lo + nu * kTile + 4 * lane;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) ent[j] = (nu < ntiles && s0 + j < hi) ? page[s0 + j] : -1;
+    };
+    auto check_run = [&](int nu) {  // tiles are asked for in order, each at most twice in a row
+      if (nu == run_tile) return;
+      run_first = __shfl_sync(0xffffffffu, ent[0], 0);
+      bool good = true;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) good = good && (ent[j] < 0 || ent[j] == run_first + 4 * lane + j);
+      run_ok = __all_sync(0xffffffffu, good) && ta.use_tma != 0;
+      run_tile = nu;
+      fetch_entries(nu + 1);
+    };
     // Request tile `nu` of K (is_k) or V once its ring slot is free.
     auto load_unit = [&](int nu, bool is_k) {
+      check_run(nu);
       const int nslots = is_k ? kKSlots : kVSlots;
       const int bar_full = is_k ? kBarKFull : kBarVFull, bar_empty = is_k ? kBarKEmpty : kBarVEmpty;
       const int slot = nu % nslots, use = nu / nslots;
       if (use > 0) ok = warp_wait(bar(bar_empty + slot), (use - 1) & 1);
       if (!ok) return;
       const uint32_t dst = (is_k ? sK : sV) + slot * kUnitBytes, full = bar(bar_full + slot);
-      if (affine) {
+      if (run_ok) {
         // one copy for all heads, or one per KV head (lane j: head hk0 + j)
         const int copies = ta.box_heads > 1 ? 1 : nkv;
         if (lane < copies) {
-          const int hk = hk0 + lane, first = slot_lo + nu * kTile;
+          const int hk = hk0 + lane, first = run_first;
           const int c1 = ta.slot_axis == 1 ? first : hk, c2 = ta.slot_axis == 1 ? hk : first;
           mbar_expect_tx(full, ta.box_heads * kHeadBytes);
           tma_load_3d(dst + lane * kHeadBytes, is_k ? &ta.tmap_k : &ta.tmap_v, 0, c1, c2, full);
@@ -676,6 +690,7 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
         }
       };
       // start: K of tile 0, table tiles 0 and 1, V of tiles 0 and 1
+      fetch_entries(0);
       load_unit(0, true);
       issue_table(0);
       load_unit(0, false);

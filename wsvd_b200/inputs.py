@@ -186,15 +186,20 @@ def make_workload(spec: WorkloadSpec, device="cuda", heads: Optional[slice] = No
                      spec.seed * 1000 + heads.indices(spec.heads)[0], device)
 
 
-def token_major_copy(case: DecodeCase, shuffle_seed: Optional[int] = None) -> DecodeCase:
+def token_major_copy(case: DecodeCase, shuffle_seed: Optional[int] = None, page_size: int = 1) -> DecodeCase:
     """Re-lay a case out in the reference's native token-major form [T, Hkv, R] with a
-    (optionally shuffled) page table; contents are identical."""
+    (optionally shuffled) page table; contents are identical.  `page_size` > 1 shuffles whole
+    pages of that many consecutive token slots (a paged cache) instead of single slots."""
     st = case.storage
     B, H, S, Rk = st["latent_k"].shape
     dev = st["latent_k"].device
     T = B * S
     perm = torch.arange(T)
-    if shuffle_seed is not None:
+    if shuffle_seed is not None and page_size > 1:
+        assert T % page_size == 0
+        pages = torch.randperm(T // page_size, generator=torch.Generator().manual_seed(shuffle_seed))
+        perm = (pages[:, None] * page_size + torch.arange(page_size)[None, :]).reshape(T)
+    elif shuffle_seed is not None:
         perm = torch.randperm(T, generator=torch.Generator().manual_seed(shuffle_seed))
     table = perm.view(B, S).to(torch.int32)
     idx = table.long().to(dev)
