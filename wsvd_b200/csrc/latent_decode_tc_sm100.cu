@@ -153,10 +153,7 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 // try_wait with a suspend-time hint: the waiting thread is parked by the hardware until
 // the phase completes or the hint (ns) expires, instead of spinning on issue slots.
 constexpr uint32_t kWaitHintNs = 20000;
-#ifndef WSVD_SPIN_SLEEP_NS
-#define WSVD_SPIN_SLEEP_NS 32
-#endif
-constexpr uint32_t kSpinSleepNs = WSVD_SPIN_SLEEP_NS;
+constexpr uint32_t kSpinSleepNs = 32;
 __device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
