@@ -181,7 +181,7 @@ def run_reference(args, spec):
     line = {
         "impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["ms_per_step_sample"], "higher_is_better": True,
-        "scaling": "strong" if args.gpus > 1 and not args.weak else "weak", "vs_baseline": None,
+        "scaling": "weak" if args.weak else "strong", "vs_baseline": None,
         "dtype": "i8 latents, f32 math", "data": "synthetic",
         "config": workload_config(spec, spec.heads // args.gpus if not args.weak else spec.heads, args.gpus),
         "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
