@@ -126,6 +126,19 @@ def test_balanced_shares_on_ragged_batches(heads, lens):
         assert_close(got, want, "balanced O")
 
 
+def test_balanced_shares_with_more_sequences_than_threads():
+    """700 sequences: the in-kernel prefix sum over the lengths runs in two chunks of 640."""
+    g = torch.Generator().manual_seed(5)
+    lens = [int(x) for x in torch.randint(0, 260, (700,), generator=g)]
+    lens[3], lens[650], lens[699] = 0, 513, 129
+    case = inputs.make_case(len(lens), 4, 128, 16, 16, lens, max(lens), seed=63)
+    c = case.to("cuda")
+    got = op_i8(c.q, c.infer_state, 4, 128, c.latent_k, c.k_scale, c.latent_v, c.v_scale, c.wk, None, wv=c.wv, kernel="tc")
+    torch.cuda.synchronize()
+    assert ops.kernel_status() == 0, "a bounded wait timed out"
+    assert_close(got, oracle_for(case, wv=True), "700 sequences")
+
+
 def test_all_sequences_empty():
     case = inputs.make_case(3, 4, 128, 64, 64, [0, 0, 0], 1, seed=62)
     c = case.to("cuda")
