@@ -498,8 +498,12 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
   // requested during set-up so that their latency is hidden behind it
   int slot_n = -1;
   unsigned short sk_raw = 0, sv_raw = 0;
+  int slot0 = -1;  // epilogue: token slot of this lane's first token
+  int ent[4];      // requesting warp: page entries of the tile it requests next (see check_run)
 
-  // ---- set-up of the item: barriers (MMA warp), first loads (the others)
+  // ---- set-up of the item: barriers (MMA warp), first loads (the others).  Nothing here waits for
+  //      a load: what was requested is used after the barrier, so that the barrier is reached after
+  //      one round trip (the sequence length) and not after the three of the page-table look-ups.
   if constexpr (!kEpi) {
   if (warp == kMmaWarp) {
     for (int i = lane; i < kNumBars; i += 32) {
@@ -514,21 +518,15 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
       mbar_init(bar(i), count);
     }
     fence_barrier_init();
+  } else if (warp == kMmaWarp + 1) {
+    // page entries of tile 0, for the run check that precedes the first copies
+    const int s0 = lo + 4 * lane;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) ent[j] = s0 + j < hi ? page[s0 + j] : -1;
   }
   } else {
   if (warp < 4 * G) {
     const int hk_pre = (h0 + (warp >> 2)) / gqa;
-    {
-      // this lane's first token: page entry and scales; and the page entry of its next token
-      const int s_first = lo + (warp & 3) * 32 + lane;
-      int slot0 = -1;
-      if (s_first < hi) slot0 = page[s_first];
-      if (s_first + kTile < hi) slot_n = page[s_first + kTile];
-      if (slot0 >= 0) {
-        sk_raw = reinterpret_cast<const unsigned short*>(p.k_scale)[(int64_t)hk_pre * p.ks_stride_h + (int64_t)slot0 * p.ks_stride_t];
-        sv_raw = reinterpret_cast<const unsigned short*>(p.v_scale)[(int64_t)hk_pre * p.vs_stride_h + (int64_t)slot0 * p.vs_stride_t];
-      }
-    }
     // the head's slice of wk for the [P;Q] build: requested now, used after the barrier
     if (wk_vec) {
       const bool il = p.rope_layout == WSVD_ROPE_INTERLEAVED;
@@ -552,6 +550,13 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
                          (int64_t)(h0 + (warp >> 2)) * p.q_stride_h;
       qpre[0] = *reinterpret_cast<const uint4*>(qp + (il ? ic * 16 : ic * 8));
       qpre[1] = *reinterpret_cast<const uint4*>(qp + (il ? ic * 16 + 8 : 64 + ic * 8));
+    }
+    {
+      // this lane's first token and its next one: page entries (the first token's scales are
+      // requested once its entry is here, after the [P;Q] build)
+      const int s_first = lo + (warp & 3) * 32 + lane;
+      if (s_first < hi) slot0 = page[s_first];
+      if (s_first + kTile < hi) slot_n = page[s_first + kTile];
     }
   }
   }
@@ -615,7 +620,6 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
     // requesting warp checks that tile by tile: lane l holds the page entries of tokens 4l..4l+3 of
     // the tile it will request next (fetched one tile ahead), and the warp votes.  `run_first`: the
     // slot of the tile's first token.
-    int ent[4];
     int run_tile = -1, run_first = 0;
     bool run_ok = false;
     auto fetch_entries = [&](int nu) {
@@ -686,8 +690,8 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
           tma_load_3d(sA + buf * kABufBytes, &ta.tmap_table, 0, pos0 + t * kTile, 0, bar(kBarAFull + buf));
         }
       };
-      // start: K of tile 0, table tiles 0 and 1, V of tiles 0 and 1
-      fetch_entries(0);
+      // start: K of tile 0, table tiles 0 and 1, V of tiles 0 and 1 (tile 0's page entries were
+      // requested before the barrier)
       load_unit(0, true);
       issue_table(0);
       load_unit(0, false);
@@ -864,6 +868,10 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(kBarPq));
+    }
+    if (slot0 >= 0) {
+      sk_raw = reinterpret_cast<const unsigned short*>(p.k_scale)[(int64_t)hk * p.ks_stride_h + (int64_t)slot0 * p.ks_stride_t];
+      sv_raw = reinterpret_cast<const unsigned short*>(p.v_scale)[(int64_t)hk * p.vs_stride_h + (int64_t)slot0 * p.vs_stride_t];
     }
 
     const __half* ksc = reinterpret_cast<const __half*>(p.k_scale) + (int64_t)hk * p.ks_stride_h;
