@@ -467,6 +467,7 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
   // The barriers of an item are re-made for the next one.  Two sets are used in turn, so that a set
   // is invalidated and re-initialised a whole item after its last use.
   for (int round = 0; tiles_left > 0 && b < p.batch; ++round) {
+  const int req = p.b_req_idx[b];  // requested together with the length: one round trip, not two
   const int n = p.b_seq_len[b];
   int lo, hi;
   int tiles_b = 0, n_parts = 1, c_first = 0;  // balanced mode: the CTAs that share this (sequence, head group)
@@ -492,7 +493,7 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
   const int ntiles = (hi - lo + kTile - 1) / kTile;
   const int pos0 = (p.pos_offset != nullptr ? p.pos_offset[b] : 0) + lo;  // RoPE position of token lo
 
-  const int32_t* page = p.req_to_token + (int64_t)p.b_req_idx[b] * p.rtt_stride;
+  const int32_t* page = p.req_to_token + (int64_t)req * p.rtt_stride;
 
   uint4 wpre[8], qpre[2];
   // requested during set-up so that their latency is hidden behind it
@@ -1079,11 +1080,24 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
         finish = verdict[0] != 0;
         if (finish) {
           const int64_t slot0 = ((int64_t)b * n_hg + hg + c_first) * kG + g;
-          float m = -INFINITY;
-          for (int i = 0; i < n_parts; ++i) m = fmaxf(m, __ldcg(a.lse + slot0 + (int64_t)i * kG));
-          float wsum = 0.f, osum = 0.f;
           const int rr = q4 * 32 + lane;  // one rank per thread of the head
-          for (int i = 0; i < n_parts; ++i) {
+          // the first four partials (a head is rarely shared by more CTAs) are requested at once
+          float ls[4], mo[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            ls[i] = i < n_parts ? __ldcg(a.lse + slot0 + (int64_t)i * kG) : -INFINITY;
+            mo[i] = i < n_parts && rr < Rv ? __ldcg(a.mid_o + (slot0 + (int64_t)i * kG) * Rv + rr) : 0.f;
+          }
+          float m = fmaxf(fmaxf(ls[0], ls[1]), fmaxf(ls[2], ls[3]));
+          for (int i = 4; i < n_parts; ++i) m = fmaxf(m, __ldcg(a.lse + slot0 + (int64_t)i * kG));
+          float wsum = 0.f, osum = 0.f;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float w = ls[i] > -INFINITY ? __expf(ls[i] - m) : 0.f;
+            wsum += w;
+            osum = fmaf(w, mo[i], osum);
+          }
+          for (int i = 4; i < n_parts; ++i) {
             const float w = __expf(__ldcg(a.lse + slot0 + (int64_t)i * kG) - m);
             wsum += w;
             if (rr < Rv) osum = fmaf(w, __ldcg(a.mid_o + (slot0 + (int64_t)i * kG) * Rv + rr), osum);
@@ -1102,10 +1116,11 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
         if (p.wv == nullptr) {
           if (d < Rv) out[d] = __float2half_rn(o_row[d]);
         } else {
-          // out[d] = sum_r O_lat[r] U_v[r, hk*128 + d]: consecutive d in consecutive lanes, four sums in flight
+          // out[d] = sum_r O_lat[r] U_v[r, hk*128 + d]: consecutive d in consecutive lanes, four sums and
+          // 32 loads of U_v (L2) in flight
           const __half* w = reinterpret_cast<const __half*>(p.wv) + (int64_t)hk * p.head_dim + d;
           float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
-#pragma unroll 4
+#pragma unroll 8
           for (int k = 0; k < Rv; k += 4) {
             y0 = fmaf(o_row[k], __half2float(__ldg(w + (int64_t)k * p.wv_stride_r)), y0);
             y1 = fmaf(o_row[k + 1], __half2float(__ldg(w + (int64_t)(k + 1) * p.wv_stride_r)), y1);
