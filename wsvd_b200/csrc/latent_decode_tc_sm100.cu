@@ -182,7 +182,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   }
 }
 // The same for a whole warp: every lane waits, and the warp agrees on the outcome so that no
-// lane leaves a loop that the others stay in.
+// lane leaves a loop that the others stay in.  (The epilogue's tile loop calls mbar_wait without
+// the vote: its lanes run in lockstep, wait on the same barrier and read the same timer, so they
+// reach the same verdict, and the three votes per tile were 1 % of the kernel's time.)
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity) {
   return __all_sync(0xffffffffu, mbar_wait(bar, parity));
 }
@@ -911,8 +913,9 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
 #pragma unroll
         for (int w4 = 0; w4 < 4; ++w4) {
           if (ref[w4] > -INFINITY) {  // (a warp without tokens in this tile has no MMA and reference -inf)
+            // the two low digit sums are combined as integers (|d| <= 32 * 255 * 128 < 2^21)
             const float v = fmaf((float)(int32_t)d[w4][2], 65536.f,
-                                 fmaf((float)(int32_t)d[w4][1], 256.f, (float)(int32_t)d[w4][0]));
+                                 (float)((int32_t)d[w4][1] * 256 + (int32_t)d[w4][0]));
             acc = fmaf(v, fast_exp2(ref[w4] - m_new) * (1.f / kPlaneScale), acc);
           }
         }
@@ -940,7 +943,7 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
       uint4 kreg[4];
       {
         const int kslot = t % kKSlots;
-        ok = warp_wait(bar(kBarKFull + kslot), (t / kKSlots) & 1);
+        ok = mbar_wait(bar(kBarKFull + kslot), (t / kKSlots) & 1);
         if (!ok) break;
         const uint32_t krows = sK + kslot * kUnitBytes + sub * kHeadBytes;
 #pragma unroll
@@ -951,7 +954,7 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(kBarKEmpty + kslot));
       }
-      ok = warp_wait(bar(kBarWFull + wb), (u / kWBufs) & 1);
+      ok = mbar_wait(bar(kBarWFull + wb), (u / kWBufs) & 1);
       if (!ok) break;
       tc_fence_after();
 
@@ -1004,7 +1007,7 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
       //      orders this warp's reads of D and of the references (and, through the MMAs' completion,
       //      the MMAs' reads of its digit planes) before the planes of this tile are written.
       if (t > 0) {
-        ok = warp_wait(bar(kBarDFull + g), (t - 1) & 1);
+        ok = mbar_wait(bar(kBarDFull + g), (t - 1) & 1);
         if (!ok) break;
         tc_fence_after();
         fold_values(t - 1);
