@@ -991,7 +991,7 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
       const float2 dsum = __fadd2_rn(dot0, dot1);
       const float sk = __half2float(__ushort_as_half(sk_raw)), sv = __half2float(__ushort_as_half(sv_raw));
       const float z = valid ? (dsum.x + dsum.y) * sk : -INFINITY;
-      const float y = (valid && sv > 0.f) ? z + fast_log2(sv) : -INFINITY;
+      const float y = valid ? z + fast_log2(sv) : -INFINITY;  // log2(0) = -inf: a zero scale drops the token's value
       sk_raw = sk_n;
       sv_raw = sv_n;
 
@@ -999,7 +999,7 @@ __device__ __forceinline__ void run_share(const TcArgs& ta, uint8_t* sm) {
       const float mz_w = warp_max_redux(z), my_w = warp_max_redux(y);
       if (mz_w > -INFINITY) {
         const float m_new = fmaxf(m_run, mz_w);
-        l_lane = l_lane * fast_exp2(m_run - m_new) + (valid ? fast_exp2(z - m_new) : 0.f);  // m_run = -inf -> factor 0
+        l_lane = fmaf(l_lane, fast_exp2(m_run - m_new), fast_exp2(z - m_new));  // 2^-inf = 0: m_run = -inf, masked tokens
         m_run = m_new;
       }
 
