@@ -144,6 +144,15 @@ size_t wsvd_latent_decode_workspace_bytes(const WsvdLatentDecodeParams* p);
 int wsvd_latent_decode(const WsvdLatentDecodeParams* p, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * The arithmetic of the balanced work distribution, exposed for tests and for hosts that want to
+ * know where a CTA's share starts: `total` tiles in the order (sequence, head group, tile) are cut
+ * into n_shares = min(CTAs, total) shares; share c is [wsvd_share_begin(c), wsvd_share_begin(c+1)),
+ * and wsvd_share_owner inverts that for 0 <= tile < total.  Pure host functions, no CUDA call.
+ */
+int64_t wsvd_share_begin(int32_t c, int64_t total, int32_t n_shares);
+int32_t wsvd_share_owner(int64_t tile, int64_t total, int32_t n_shares);
+
+/*
  * wsvd_latent_decode without the merge: stage 1 with the work distribution the whole op uses,
  * the partials left in `workspace` in the library's own layout.  For timing the dominant kernel
  * alone; p->out is not written and may be NULL.

@@ -169,6 +169,8 @@ SYMBOLS = {
     "wsvd_latent_decode_plan": (ctypes.c_int, [_P, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]),
     "wsvd_latent_decode_workspace_bytes": (ctypes.c_size_t, [_P]),
     "wsvd_latent_decode": (ctypes.c_int, [_P, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    "wsvd_share_begin": (ctypes.c_int64, [ctypes.c_int32, ctypes.c_int64, ctypes.c_int32]),
+    "wsvd_share_owner": (ctypes.c_int32, [ctypes.c_int64, ctypes.c_int64, ctypes.c_int32]),
     "wsvd_latent_decode_partials": (ctypes.c_int, [_P, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
     "wsvd_dense_decode_workspace_bytes": (ctypes.c_size_t, [ctypes.POINTER(DenseDecodeParams)]),
     "wsvd_dense_decode_f16": (ctypes.c_int, [ctypes.POINTER(DenseDecodeParams), ctypes.c_void_p, ctypes.c_size_t,

@@ -347,6 +347,13 @@ int wsvd_latent_decode(const WsvdLatentDecodeParams* p, void* workspace, size_t 
   return decode_impl(p, nullptr, workspace, workspace_bytes, stream);
 }
 
+int64_t wsvd_share_begin(int32_t c, int64_t total, int32_t n_shares) {
+  return n_shares > 0 ? wsvd::share_begin(c, total, n_shares) : 0;
+}
+int32_t wsvd_share_owner(int64_t tile, int64_t total, int32_t n_shares) {
+  return total > 0 ? wsvd::share_owner(tile, total, n_shares) : 0;
+}
+
 int wsvd_latent_decode_partials(const WsvdLatentDecodeParams* p, void* workspace, size_t workspace_bytes,
                                 void* stream) {
   return decode_impl(p, nullptr, workspace, workspace_bytes, stream, false);
