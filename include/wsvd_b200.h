@@ -239,16 +239,21 @@ int wsvd_latent_quant_append_i8(const WsvdQuantAppendParams* p, void* stream);
  * Element-wise pieces of the decode step around the attention op, one kernel each (in the
  * reference's accuracy pipeline they are chains of small torch ops: LlamaRMSNorm,
  * apply_rotary_pos_emb and the MLP's act_fn * up, fake_quant/svd_utils.py:1628-1674).  f16 in
- * and out, contiguous rows, fp32 arithmetic.
- *  - wsvd_rms_norm_f16: y[r,:] = x[r,:] * rsqrt(mean(x[r,:]^2) + eps), no weight vector.
- *  - wsvd_rope_half_f16: in place on q [batch, heads, head_dim]: the pairs (i, i + head_dim/2)
- *    are rotated by pos[b] * inv_freq[i] (inv_freq: head_dim/2 floats on the device).
- *  - wsvd_silu_mul_f16: out[i] = up[i] * silu(gate[i]), silu rounded to f16 before the product.
+ * and out, fp32 arithmetic; strides in elements, so that the inputs may be column slices of one
+ * wider GEMM output (q | k | v, or up | gate).
+ *  - wsvd_rms_norm_f16: y[r,:] = x[r,:] * rsqrt(mean(x[r,:]^2) + eps), no weight vector;
+ *    contiguous rows.
+ *  - wsvd_rope_half_f16: in place on q [batch, heads, head_dim] with q_stride_b elements between
+ *    sequences (heads contiguous inside a sequence): the pairs (i, i + head_dim/2) are rotated by
+ *    pos[b] * inv_freq[i] (inv_freq: head_dim/2 floats on the device).
+ *  - wsvd_silu_mul_f16: out[r,c] = up[r,c] * silu(gate[r,c]), silu rounded to f16 before the
+ *    product; up and gate [rows, cols] with leading dimensions up_ld, gate_ld; out contiguous.
  */
 int wsvd_rms_norm_f16(const void* x, void* y, int32_t rows, int32_t cols, float eps, void* stream);
-int wsvd_rope_half_f16(void* q, const int32_t* pos, const float* inv_freq, int32_t batch, int32_t heads,
-                       int32_t head_dim, void* stream);
-int wsvd_silu_mul_f16(const void* up, const void* gate, void* out, int64_t n, void* stream);
+int wsvd_rope_half_f16(void* q, int64_t q_stride_b, const int32_t* pos, const float* inv_freq, int32_t batch,
+                       int32_t heads, int32_t head_dim, void* stream);
+int wsvd_silu_mul_f16(const void* up, int64_t up_ld, const void* gate, int64_t gate_ld, void* out, int32_t rows,
+                      int32_t cols, void* stream);
 
 /*
  * Head-sharded multi-GPU decode with the all-gather fused into the op's own kernels.

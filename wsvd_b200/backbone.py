@@ -104,6 +104,13 @@ class LatentDecoder:
                 L.Wo = L.Wo[rank * Hl * spec.head_dim:(rank + 1) * Hl * spec.head_dim].contiguous()
             L.Wup = gauss(spec.hidden, spec.ffn // world, s)
             L.Wgate = gauss(spec.hidden, spec.ffn // world, s)
+            # one GEMM for the three projections of the normalised input, one for up | gate: the
+            # weights live concatenated and the separate names are column slices of them
+            L.Wqkv = torch.cat([L.Wq, L.A_k, L.A_v], dim=1).contiguous()
+            L.Wug = torch.cat([L.Wup, L.Wgate], dim=1).contiguous()
+            nq, nk, nf = L.Wq.shape[1], L.A_k.shape[1], L.Wup.shape[1]
+            L.Wq, L.A_k, L.A_v = L.Wqkv[:, :nq], L.Wqkv[:, nq:nq + nk], L.Wqkv[:, nq + nk:]
+            L.Wup, L.Wgate = L.Wug[:, :nf], L.Wug[:, nf:]
             L.Wdown = gauss(spec.ffn // world, spec.hidden, 1.0 / math.sqrt(spec.ffn))
             # head-major latent cache [B, Hl, S, R] seen as the token-major strided view the op takes
             L.k_store = torch.randint(-127, 128, (batch, Hl, S, spec.rank_k), generator=gen, device=dev,
@@ -188,11 +195,18 @@ class LatentDecoder:
         if self.world > 1:
             import torch.distributed as dist
         for L in self.layers:
-            xn = ops.rms_norm(x) if fe else _rms_norm(x)
-            q = (xn @ L.Wq).view(B, Hl, sp.head_dim)
-            q = ops.rope_half_(q, pos, self.inv_freq) if fe else rope_half(q, pos, sp.theta)
-            xk = (xn @ L.A_k).view(B, Hl, sp.rank_k)
-            xv = (xn @ L.A_v).view(B, Hl, sp.rank_v)
+            if fe:
+                xn = ops.rms_norm(x)
+                qkv = xn @ L.Wqkv  # [B, Hl*D | Hl*Rk | Hl*Rv]: the three outputs are column slices
+                nq, nk = Hl * sp.head_dim, Hl * sp.rank_k
+                q = ops.rope_half_(qkv[:, :nq].unflatten(1, (Hl, sp.head_dim)), pos, self.inv_freq)
+                xk = qkv[:, nq:nq + nk].unflatten(1, (Hl, sp.rank_k))
+                xv = qkv[:, nq + nk:].unflatten(1, (Hl, sp.rank_v))
+            else:
+                xn = _rms_norm(x)
+                q = rope_half((xn @ L.Wq).view(B, Hl, sp.head_dim), pos, sp.theta)
+                xk = (xn @ L.A_k).view(B, Hl, sp.rank_k)
+                xv = (xn @ L.A_v).view(B, Hl, sp.rank_v)
             ops.latent_quant_append(xk, xv, self.before, L.lk, L.ks, L.lv, L.vs)
             o = self._attend(L, q)
             if self.o_proj == "row":
@@ -201,9 +215,13 @@ class LatentDecoder:
                 x = x + a
             else:
                 x = x + o @ L.Wo
-            h = ops.rms_norm(x) if fe else _rms_norm(x)
-            up, gate = h @ L.Wup, h @ L.Wgate
-            f = (ops.silu_mul(up, gate) if fe else up * torch.nn.functional.silu(gate)) @ L.Wdown
+            if fe:
+                ug = ops.rms_norm(x) @ L.Wug
+                nf = L.Wup.shape[1]
+                f = ops.silu_mul(ug[:, :nf], ug[:, nf:]) @ L.Wdown
+            else:
+                h = _rms_norm(x)
+                f = ((h @ L.Wup) * torch.nn.functional.silu(h @ L.Wgate)) @ L.Wdown
             if self.world > 1:
                 dist.all_reduce(f, group=self.group)
             x = x + f

@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const __half* __restrict_
 }
 
 // half-split rotary embedding in place: q[b, h, i], q[b, h, i + D/2] rotated by pos[b] * inv_freq[i]
-__global__ void rope_half_kernel(__half* __restrict__ q, const int32_t* __restrict__ pos,
+__global__ void rope_half_kernel(__half* __restrict__ q, int64_t q_stride_b, const int32_t* __restrict__ pos,
                                  const float* __restrict__ inv_freq, int heads, int half_dim, int64_t total) {
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
@@ -39,20 +39,21 @@ __global__ void rope_half_kernel(__half* __restrict__ q, const int32_t* __restri
   const int b = (int)(bh / heads);
   float sn, cs;
   sincosf((float)pos[b] * inv_freq[i], &sn, &cs);
-  __half* row = q + bh * (2 * half_dim);
+  __half* row = q + (int64_t)b * q_stride_b + (bh - (int64_t)b * heads) * (2 * half_dim);
   const float lo = __half2float(row[i]), hi = __half2float(row[i + half_dim]);
   row[i] = __float2half_rn(lo * cs - hi * sn);
   row[i + half_dim] = __float2half_rn(hi * cs + lo * sn);
 }
 
 // out = up * f16(silu(gate)), the product rounded to f16 (the two roundings of the torch chain)
-__global__ void silu_mul_kernel(const __half* __restrict__ up, const __half* __restrict__ gate, __half* __restrict__ out,
-                                int64_t n) {
+__global__ void silu_mul_kernel(const __half* __restrict__ up, int64_t up_ld, const __half* __restrict__ gate,
+                                int64_t gate_ld, __half* __restrict__ out, int cols, int64_t n) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
-  const float g = __half2float(gate[i]);
+  const int64_t r = i / cols, c = i - r * cols;
+  const float g = __half2float(gate[r * gate_ld + c]);
   const __half s = __float2half_rn(g / (1.f + expf(-g)));
-  out[i] = __float2half_rn(__half2float(up[i]) * __half2float(s));
+  out[i] = __float2half_rn(__half2float(up[r * up_ld + c]) * __half2float(s));
 }
 
 }  // namespace
@@ -70,24 +71,29 @@ int wsvd_rms_norm_f16(const void* x, void* y, int32_t rows, int32_t cols, float 
   return e == cudaSuccess ? WSVD_OK : wsvd::record_cuda_error(e);
 }
 
-int wsvd_rope_half_f16(void* q, const int32_t* pos, const float* inv_freq, int32_t batch, int32_t heads,
-                       int32_t head_dim, void* stream) {
+int wsvd_rope_half_f16(void* q, int64_t q_stride_b, const int32_t* pos, const float* inv_freq, int32_t batch,
+                       int32_t heads, int32_t head_dim, void* stream) {
   if (!q || !pos || !inv_freq) return WSVD_ERR_NULL_POINTER;
   if (batch < 0 || heads <= 0 || head_dim <= 0 || head_dim % 2) return WSVD_ERR_BAD_SHAPE;
+  if (q_stride_b < (int64_t)heads * head_dim) return WSVD_ERR_BAD_STRIDE;
   const int64_t total = (int64_t)batch * heads * (head_dim / 2);
   if (total == 0) return WSVD_OK;
   wsvd::rope_half_kernel<<<(unsigned)((total + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<__half*>(q), pos, inv_freq, heads, head_dim / 2, total);
+      reinterpret_cast<__half*>(q), q_stride_b, pos, inv_freq, heads, head_dim / 2, total);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? WSVD_OK : wsvd::record_cuda_error(e);
 }
 
-int wsvd_silu_mul_f16(const void* up, const void* gate, void* out, int64_t n, void* stream) {
+int wsvd_silu_mul_f16(const void* up, int64_t up_ld, const void* gate, int64_t gate_ld, void* out, int32_t rows,
+                      int32_t cols, void* stream) {
   if (!up || !gate || !out) return WSVD_ERR_NULL_POINTER;
-  if (n < 0) return WSVD_ERR_BAD_SHAPE;
+  if (rows < 0 || cols <= 0) return WSVD_ERR_BAD_SHAPE;
+  if (up_ld < cols || gate_ld < cols) return WSVD_ERR_BAD_STRIDE;
+  const int64_t n = (int64_t)rows * cols;
   if (n == 0) return WSVD_OK;
   wsvd::silu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const __half*>(up), reinterpret_cast<const __half*>(gate), reinterpret_cast<__half*>(out), n);
+      reinterpret_cast<const __half*>(up), up_ld, reinterpret_cast<const __half*>(gate), gate_ld,
+      reinterpret_cast<__half*>(out), cols, n);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? WSVD_OK : wsvd::record_cuda_error(e);
 }

@@ -447,24 +447,26 @@ def rms_norm(x: torch.Tensor, eps: float = 1e-5, out: Optional[torch.Tensor] = N
 
 def rope_half_(q: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor, stream=None) -> torch.Tensor:
     """Half-split rotary embedding of q [B, H, D] f16 in place at positions pos [B] int32;
-    inv_freq [D/2] f32 on the device."""
+    inv_freq [D/2] f32 on the device.  q may be a column slice of a wider matrix (any stride between
+    sequences; the heads of a sequence are contiguous)."""
     _cuda_tensor("q", q, (torch.float16,), 3)
     _cuda_tensor("pos", pos, (torch.int32,), 1)
     _cuda_tensor("inv_freq", inv_freq, (torch.float32,), 1)
-    _need(q.is_contiguous() and pos.numel() == q.shape[0] and inv_freq.numel() * 2 == q.shape[2],
-          "q must be contiguous [B, H, D] with B positions and D/2 frequencies")
-    check(_lib.lib().wsvd_rope_half_f16(_ptr(q), _ptr(pos), _ptr(inv_freq), q.shape[0], q.shape[1], q.shape[2],
-                                        _stream(stream)), "wsvd_rope_half_f16")
+    _need(q.stride(1) == q.shape[2] and pos.numel() == q.shape[0] and inv_freq.numel() * 2 == q.shape[2],
+          "q must be [B, H, D] with contiguous heads, B positions and D/2 frequencies")
+    check(_lib.lib().wsvd_rope_half_f16(_ptr(q), q.stride(0), _ptr(pos), _ptr(inv_freq), q.shape[0], q.shape[1],
+                                        q.shape[2], _stream(stream)), "wsvd_rope_half_f16")
     return q
 
 
 def silu_mul(up: torch.Tensor, gate: torch.Tensor, out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
-    """up * silu(gate), f16, same shape."""
-    _cuda_tensor("up", up, (torch.float16,), up.dim())
-    _cuda_tensor("gate", gate, (torch.float16,), up.dim())
-    _need(up.shape == gate.shape and up.is_contiguous() and gate.is_contiguous(), "up and gate: same contiguous shape")
+    """up * silu(gate), f16 [rows, cols]; up and gate may be column slices of one wider matrix."""
+    _cuda_tensor("up", up, (torch.float16,), 2)
+    _cuda_tensor("gate", gate, (torch.float16,), 2)
+    _need(up.shape == gate.shape, "up and gate must have the same shape")
     if out is None:
-        out = torch.empty_like(up)
-    check(_lib.lib().wsvd_silu_mul_f16(_ptr(up), _ptr(gate), _ptr(out), up.numel(), _stream(stream)),
-          "wsvd_silu_mul_f16")
+        out = torch.empty(up.shape, dtype=up.dtype, device=up.device)
+    _need(out.is_contiguous() and out.shape == up.shape, "out must be contiguous and shaped like up")
+    check(_lib.lib().wsvd_silu_mul_f16(_ptr(up), up.stride(0), _ptr(gate), gate.stride(0), _ptr(out), up.shape[0],
+                                       up.shape[1], _stream(stream)), "wsvd_silu_mul_f16")
     return out
