@@ -139,6 +139,24 @@ def test_balanced_shares_with_more_sequences_than_threads():
     assert_close(got, oracle_for(case, wv=True), "700 sequences")
 
 
+def test_rank_62_reaches_the_tensor_core_path_by_zero_padding():
+    """The accuracy pipeline's uniform rank is 62 (fake_quant/local_ft_grad_utils.py:2475-2478): not a
+    multiple of 16, so the unpadded cache runs on the generic kernel; stored zero-padded to 64 it runs on
+    the tensor-core kernel, with the same result."""
+    lens = [1300, 40, 777]
+    case = inputs.make_case(len(lens), 8, 128, 62, 62, lens, 1300, seed=67)
+    want = oracle_for(case, wv=True)
+    c = case.to("cuda")
+    got_generic = op_i8(c.q, c.infer_state, 8, 128, c.latent_k, c.k_scale, c.latent_v, c.v_scale, c.wk, None, wv=c.wv)
+    padded = inputs.padded_rank_copy(case, 64, 64).to("cuda")
+    got_tc = op_i8(padded.q, padded.infer_state, 8, 128, padded.latent_k, padded.k_scale, padded.latent_v,
+                   padded.v_scale, padded.wk, None, wv=padded.wv, kernel="tc")
+    torch.cuda.synchronize()
+    assert ops.kernel_status() == 0
+    assert_close(got_generic, want, "rank 62, generic kernel")
+    assert_close(got_tc, want, "rank 62 padded to 64, tensor-core kernel")
+
+
 def test_all_sequences_empty():
     case = inputs.make_case(3, 4, 128, 64, 64, [0, 0, 0], 1, seed=62)
     c = case.to("cuda")

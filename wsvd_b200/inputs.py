@@ -186,6 +186,25 @@ def make_workload(spec: WorkloadSpec, device="cuda", heads: Optional[slice] = No
                      spec.seed * 1000 + heads.indices(spec.heads)[0], device)
 
 
+def padded_rank_copy(case: DecodeCase, rank_k: int, rank_v: int) -> DecodeCase:
+    """The same case with its latents and up-projection factors zero-padded to (rank_k, rank_v):
+    how a cache of rank 62 (the accuracy pipeline's uniform rank) is stored to reach the
+    tensor-core path, which takes ranks that are multiples of 16.  The padded ranks contribute
+    exact zeros, so the result is unchanged."""
+    st = case.storage
+    assert st, "needs the head-major storage of make_case"
+    B, H, S, Rk = st["latent_k"].shape
+    Rv = st["latent_v"].shape[3]
+    assert rank_k >= Rk and rank_v >= Rv
+    pad = torch.nn.functional.pad
+    st2 = dict(st)
+    st2["latent_k"] = pad(st["latent_k"], (0, rank_k - Rk)).contiguous()
+    st2["latent_v"] = pad(st["latent_v"], (0, rank_v - Rv)).contiguous()
+    wk = pad(case.wk, (0, 0, 0, rank_k - Rk)).contiguous()
+    wv = pad(case.wv, (0, 0, 0, rank_v - Rv)).contiguous()
+    return _assemble(st2, case.q, wk, wv, case.seq_lens, case.infer_state.max_len_in_batch, st["latent_k"].device)
+
+
 def token_major_copy(case: DecodeCase, shuffle_seed: Optional[int] = None, page_size: int = 1) -> DecodeCase:
     """Re-lay a case out in the reference's native token-major form [T, Hkv, R] with a
     (optionally shuffled) page table; contents are identical.  `page_size` > 1 shuffles whole
