@@ -1,6 +1,6 @@
-// Split-KV stage 1 of the latent decode attention on the Blackwell tensor cores
-// (tcgen05.mma with accumulators in tensor memory), for head_dim 128, int8 latents,
-// rank_k and rank_v in {16,32,48,64}.
+// The latent decode attention on the Blackwell tensor cores (tcgen05.mma with accumulators in
+// tensor memory), for head_dim 128, int8 latents, rank_k and rank_v in {16,32,48,64}: split-KV
+// stage 1 and, in the balanced mode, also the merge, the U_v projection and the head all-gather.
 //
 // Scores.  For one head, query q and position s
 //   z_s = c * sk_s * sum_r Lk[s,r] * W[s,r],
@@ -12,7 +12,7 @@
 //   [128 positions x 128 (cos|sin)] x [128 x 64*(heads of a pair)]
 // per tile of 128 positions and pair of heads: the A operand is a tile of a position table
 // of cos/sin values (f16, shared by every head and sequence, read from L2 by TMA), the B
-// operand [P;Q] is built once per CTA and stays in shared memory, the accumulator is fp32
+// operand [P;Q] is built once per work item and stays in shared memory, the accumulator is fp32
 // in tensor memory (three 128-column buffers).  Each epilogue thread owns one token: it
 // reads its row of W from tensor memory and dots it in fp32 with the token's int8 K row,
 // which it copied from the K ring into registers at the top of the tile (so that the ring
@@ -25,7 +25,7 @@
 // their owner threads as three unsigned 8-bit digit planes of round(a_s * (2^24 - 256));
 // the int32 accumulator (64 ranks x 8 columns per head) is read back once per tile and
 // folded into a running fp32 sum under a running reference max(y).  The weights lose nothing
-// that fp32 would keep: 24 bits relative to the largest weight of the tile.  The softmax
+// that fp32 would keep: 24 bits relative to the largest weight of the warp's 32 tokens.  The softmax
 // denominator is accumulated by the owner threads in fp32.
 //
 // Work.  A work item is a run of consecutive tiles of one (sequence, group of 4 heads); it ends
@@ -41,8 +41,9 @@
 //    With arrival counters (one per (sequence, head), zeroed before the launch) the kernel is the
 //    whole op: the CTA that completes a head's last partial merges the partials, multiplies by
 //    the head's slice of U_v and writes the output row; an item that one CTA covers alone skips
-//    the partials altogether.  Without counters the partials and the prefix sums are left for
-//    the merge kernel.
+//    the partials altogether.  With a peer set on top, the row goes to every rank's gathered
+//    buffer (16-byte peer stores) and the CTA that exits last runs the group's barrier.  Without
+//    counters the partials and the prefix sums are left for the merge kernel.
 //  - Split mode (no plan): CTA blockIdx.x handles split blockIdx.x % n_splits of a fixed-length
 //    split plan, partials in the [B, Hq, n_splits] layout of the reference's stage 1.
 // 20 warps:
