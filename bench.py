@@ -339,8 +339,9 @@ def run_c5(args):
                          "attention_bytes_per_step": model.attention_bytes(), "traffic": None},
             "e2e": {"value": B / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
-            # this package's kernels per layer: quantise-and-append, decode (+ RMSNorm x2, RoPE, SiLU*up)
-            "gpu_launches": steps * spec.layers * (2 + (0 if args.torch_elementwise else 4)),
+            # this package's kernels per layer: quantise-and-append, decode (+ residual-add+RMSNorm x2,
+            # RoPE, SiLU*up), and the first layer's RMSNorm once per step
+            "gpu_launches": steps * (spec.layers * 2 if args.torch_elementwise else spec.layers * 6 + 1),
             "kernel_status": int(status.item()), "clocks": clocks,
         }), flush=True)
     if world > 1:

@@ -243,6 +243,8 @@ int wsvd_latent_quant_append_i8(const WsvdQuantAppendParams* p, void* stream);
  * wider GEMM output (q | k | v, or up | gate).
  *  - wsvd_rms_norm_f16: y[r,:] = x[r,:] * rsqrt(mean(x[r,:]^2) + eps), no weight vector;
  *    contiguous rows.
+ *  - wsvd_add_rms_norm_f16: x_out = x + delta (rounded to f16), y = RMSNorm(x_out): the residual
+ *    update and the next block's normalisation in one pass; x_out may alias x.
  *  - wsvd_rope_half_f16: in place on q [batch, heads, head_dim] with q_stride_b elements between
  *    sequences (heads contiguous inside a sequence): the pairs (i, i + head_dim/2) are rotated by
  *    pos[b] * inv_freq[i] (inv_freq: head_dim/2 floats on the device).
@@ -250,6 +252,8 @@ int wsvd_latent_quant_append_i8(const WsvdQuantAppendParams* p, void* stream);
  *    product; up and gate [rows, cols] with leading dimensions up_ld, gate_ld; out contiguous.
  */
 int wsvd_rms_norm_f16(const void* x, void* y, int32_t rows, int32_t cols, float eps, void* stream);
+int wsvd_add_rms_norm_f16(const void* x, const void* delta, void* x_out, void* y, int32_t rows, int32_t cols, float eps,
+                          void* stream);
 int wsvd_rope_half_f16(void* q, int64_t q_stride_b, const int32_t* pos, const float* inv_freq, int32_t batch,
                        int32_t heads, int32_t head_dim, void* stream);
 int wsvd_silu_mul_f16(const void* up, int64_t up_ld, const void* gate, int64_t gate_ld, void* out, int32_t rows,

@@ -91,6 +91,11 @@ def test_elementwise_kernels_match_the_torch_chains():
     got, want = ops.rms_norm(x), _rms_norm(x)
     assert (got.float() - want.float()).abs().max().item() <= 2e-3  # one f16 ulp near 2: the row sums differ in order
 
+    d = (torch.randn(5, 4096, generator=g, device="cuda") * 0.3).to(torch.float16)
+    xs, ys = ops.add_rms_norm(x, d)
+    assert torch.equal(xs, x + d)
+    assert (ys.float() - _rms_norm(x + d).float()).abs().max().item() <= 2e-3
+
     q = (torch.randn(5, 6, 128, generator=g, device="cuda")).to(torch.float16)
     pos = torch.tensor([0, 1, 77, 4095, 31999], dtype=torch.int32, device="cuda")
     inv = 10000.0 ** (-torch.arange(0, 128, 2, device="cuda", dtype=torch.float32) / 128)

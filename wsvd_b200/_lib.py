@@ -186,6 +186,8 @@ SYMBOLS = {
     "wsvd_latent_quant_append_i8": (ctypes.c_int, [ctypes.POINTER(QuantAppendParams), ctypes.c_void_p]),
     "wsvd_rms_norm_f16": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32,
                                          ctypes.c_float, ctypes.c_void_p]),
+    "wsvd_add_rms_norm_f16": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                             ctypes.c_int32, ctypes.c_int32, ctypes.c_float, ctypes.c_void_p]),
     "wsvd_rope_half_f16": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p,
                                           ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p]),
     "wsvd_silu_mul_f16": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64,

@@ -194,9 +194,9 @@ class LatentDecoder:
         fe = self.fused_elementwise
         if self.world > 1:
             import torch.distributed as dist
+        xn = ops.rms_norm(x) if fe else None  # later layers get theirs from the residual add of the FFN
         for L in self.layers:
             if fe:
-                xn = ops.rms_norm(x)
                 qkv = xn @ L.Wqkv  # [B, Hl*D | Hl*Rk | Hl*Rv]: the three outputs are column slices
                 nq, nk = Hl * sp.head_dim, Hl * sp.rank_k
                 q = ops.rope_half_(qkv[:, :nq].unflatten(1, (Hl, sp.head_dim)), pos, self.inv_freq)
@@ -209,22 +209,24 @@ class LatentDecoder:
                 xv = (xn @ L.A_v).view(B, Hl, sp.rank_v)
             ops.latent_quant_append(xk, xv, self.before, L.lk, L.ks, L.lv, L.vs)
             o = self._attend(L, q)
+            a = o @ L.Wo
             if self.o_proj == "row":
-                a = o @ L.Wo
                 dist.all_reduce(a, group=self.group)
-                x = x + a
-            else:
-                x = x + o @ L.Wo
             if fe:
-                ug = ops.rms_norm(x) @ L.Wug
+                x, h = ops.add_rms_norm(x, a)  # residual add + the FFN's normalisation
+                ug = h @ L.Wug
                 nf = L.Wup.shape[1]
                 f = ops.silu_mul(ug[:, :nf], ug[:, nf:]) @ L.Wdown
             else:
+                x = x + a
                 h = _rms_norm(x)
                 f = ((h @ L.Wup) * torch.nn.functional.silu(h @ L.Wgate)) @ L.Wdown
             if self.world > 1:
                 dist.all_reduce(f, group=self.group)
-            x = x + f
+            if fe:
+                x, xn = ops.add_rms_norm(x, f)  # residual add + the next layer's normalisation
+            else:
+                x = x + f
         return x
 
     def capture(self, x: torch.Tensor):

@@ -29,6 +29,31 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const __half* __restrict_
   for (int i = threadIdx.x; i < cols; i += 256) yr[i] = __float2half_rn(__half2float(xr[i]) * scale);
 }
 
+// x_out[r, :] = f16(x[r, :] + delta[r, :]) (the residual add), y[r, :] = RMSNorm of the rounded sum:
+// the residual update and the next block's normalisation in one pass over the row
+__global__ void __launch_bounds__(256) add_rms_norm_kernel(const __half* __restrict__ x, const __half* __restrict__ delta,
+                                                           __half* __restrict__ x_out, __half* __restrict__ y, int cols,
+                                                           float eps) {
+  const int64_t off = (int64_t)blockIdx.x * cols;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < cols; i += 256) {
+    const __half sum = __float2half_rn(__half2float(x[off + i]) + __half2float(delta[off + i]));
+    x_out[off + i] = sum;
+    const float v = __half2float(sum);
+    ss = fmaf(v, v, ss);
+  }
+  ss = warp_sum(ss);
+  __shared__ float part[8];
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) tot += part[w];
+  const float scale = rsqrtf(tot / (float)cols + eps);
+  // each thread re-reads the elements it wrote itself
+  for (int i = threadIdx.x; i < cols; i += 256) y[off + i] = __float2half_rn(__half2float(x_out[off + i]) * scale);
+}
+
 // half-split rotary embedding in place: q[b, h, i], q[b, h, i + D/2] rotated by pos[b] * inv_freq[i]
 __global__ void rope_half_kernel(__half* __restrict__ q, int64_t q_stride_b, const int32_t* __restrict__ pos,
                                  const float* __restrict__ inv_freq, int heads, int half_dim, int64_t total) {
@@ -67,6 +92,18 @@ int wsvd_rms_norm_f16(const void* x, void* y, int32_t rows, int32_t cols, float 
   if (rows == 0) return WSVD_OK;
   wsvd::rms_norm_kernel<<<rows, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __half*>(x), reinterpret_cast<__half*>(y), cols, eps);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? WSVD_OK : wsvd::record_cuda_error(e);
+}
+
+int wsvd_add_rms_norm_f16(const void* x, const void* delta, void* x_out, void* y, int32_t rows, int32_t cols, float eps,
+                          void* stream) {
+  if (!x || !delta || !x_out || !y) return WSVD_ERR_NULL_POINTER;
+  if (rows < 0 || cols <= 0) return WSVD_ERR_BAD_SHAPE;
+  if (rows == 0) return WSVD_OK;
+  wsvd::add_rms_norm_kernel<<<rows, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __half*>(x), reinterpret_cast<const __half*>(delta), reinterpret_cast<__half*>(x_out),
+      reinterpret_cast<__half*>(y), cols, eps);
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? WSVD_OK : wsvd::record_cuda_error(e);
 }

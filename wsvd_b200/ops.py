@@ -445,6 +445,18 @@ def rms_norm(x: torch.Tensor, eps: float = 1e-5, out: Optional[torch.Tensor] = N
     return out
 
 
+def add_rms_norm(x: torch.Tensor, delta: torch.Tensor, eps: float = 1e-5, stream=None):
+    """(x + delta, RMSNorm(x + delta)) for x, delta [rows, cols] f16: the residual update and the
+    next block's normalisation as one kernel."""
+    _cuda_tensor("x", x, (torch.float16,), 2)
+    _cuda_tensor("delta", delta, (torch.float16,), 2)
+    _need(x.is_contiguous() and delta.is_contiguous() and x.shape == delta.shape, "x and delta: same contiguous shape")
+    x_out, y = torch.empty_like(x), torch.empty_like(x)
+    check(_lib.lib().wsvd_add_rms_norm_f16(_ptr(x), _ptr(delta), _ptr(x_out), _ptr(y), x.shape[0], x.shape[1],
+                                           float(eps), _stream(stream)), "wsvd_add_rms_norm_f16")
+    return x_out, y
+
+
 def rope_half_(q: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor, stream=None) -> torch.Tensor:
     """Half-split rotary embedding of q [B, H, D] f16 in place at positions pos [B] int32;
     inv_freq [D/2] f32 on the device.  q may be a column slice of a wider matrix (any stride between
