@@ -395,7 +395,7 @@ class Measurement:
         self.split_len, self.n_splits = ops.plan(self.p)
         # c1..c4 are shapes the tensor-core kernel accepts: without a split length from the caller the
         # library then deals the batch's tiles out in equal shares, one persistent CTA per SM
-        self.balanced = args.split_len == 0 and args.kernel != "generic"
+        self.balanced = args.split_len == 0 and args.kernel in ("auto", "tc")
         self.distribution = ("equal shares of 128-position tiles, one persistent CTA per SM" if self.balanced
                              else "fixed-length splits, one CTA per (split, 4 heads, sequence)")
         self.ws = torch.empty((ops.workspace_bytes(self.p) + 3) // 4, dtype=torch.float32, device=dev)
@@ -583,7 +583,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--kernel", default="auto", choices=["auto", "generic", "tc"])
+    ap.add_argument("--kernel", default="auto", choices=["auto", "generic", "tc", "mma"])
     ap.add_argument("--split-len", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--weak", action="store_true",
@@ -687,6 +687,8 @@ def main():
         }
         if world == 1 and not args.no_dense:
             line["dense_f16_baseline"] = dense_baseline(m, spec, ms_step, max(5, args.steps // 2))
+        if world == 1 and not args.no_extra:
+            line["f16_latents"] = f16_latents_leg(m, spec, peak, max(5, args.steps // 2))
     m.close()
 
     # ---- the head-sharded workloads (c3, c4) at this N, fewer steps ----
@@ -749,6 +751,48 @@ def dense_baseline(m, spec, ms_step, k):
     return {"us_per_layer": ms_dense * 1e3, "GB/s": dense_bytes / (ms_dense * 1e-3) / 1e9,
             "bytes_per_token_head": 4 * D, "latent_speedup": ms_dense / ms_step,
             "byte_reduction": 4 * D / (spec.rank_k + spec.rank_v + 4)}
+
+
+def f16_latents_leg(m, spec, peak, k):
+    """The same shape with an f16 latent cache (the reference's f16 op, 2*(rank_k+rank_v) bytes per
+    token-head, no scales): the warp-MMA kernel with fixed-length splits, then the merge kernel."""
+    import ctypes as ct
+
+    from wsvd_b200 import _lib, inputs, ops
+
+    case = inputs.make_case(m.B, m.H, m.D, spec.rank_k, spec.rank_v, m.lens, spec.max_len, spec.seed + 1,
+                            device=m.dev, latent_dtype=torch.float16)
+    st = case.infer_state
+    out = torch.empty(m.B, m.H, m.D, dtype=torch.float16, device=m.dev)
+    p, _keep = ops.build_params(case.q, st.b_seq_len, st.b_req_idx, st.req_manager.req_to_token_indexs,
+                                st.max_len_in_batch, case.latent_k, None, case.latent_v, None, case.wk, None,
+                                wv=case.wv, out=out)
+    split_len, n_splits = ops.plan(p)
+    ws = torch.empty((ops.workspace_bytes(p) + 3) // 4, dtype=torch.float32, device=m.dev)
+    lib, stream = _lib.lib(), torch.cuda.current_stream()
+
+    def call(fn, name):
+        _lib.check(fn(ct.byref(p), ct.c_void_p(ws.data_ptr()), ws.numel() * 4, ct.c_void_p(stream.cuda_stream)), name)
+
+    full = lambda: call(lib.wsvd_latent_decode, "wsvd_latent_decode")
+    stage1 = lambda: call(lib.wsvd_latent_decode_partials, "wsvd_latent_decode_partials")
+    for _ in range(3):
+        full()
+        stage1()
+    ms_full = m.timed(full, k) / k
+    ms_s1 = m.timed(stage1, k) / k
+    # the CUDA-core kernel on the same cache, for scale
+    p.kernel = ops.KERNEL["generic"]
+    ws_g = torch.empty((ops.workspace_bytes(p) + 3) // 4, dtype=torch.float32, device=m.dev)
+    generic = lambda: _lib.check(lib.wsvd_latent_decode(ct.byref(p), ct.c_void_p(ws_g.data_ptr()), ws_g.numel() * 4,
+                                                        ct.c_void_p(stream.cuda_stream)), "wsvd_latent_decode")
+    generic()
+    ms_generic = m.timed(generic, 3) / 3
+    nbytes = sum(m.lens) * m.H * 2 * (spec.rank_k + spec.rank_v)
+    return {"kernel": "warp-MMA (mma.sync m16n8k16), fixed-length splits", "split_len": split_len, "n_splits": n_splits,
+            "bytes_per_token_head": 2 * (spec.rank_k + spec.rank_v), "us_per_layer": ms_full * 1e3,
+            "us_stage1": ms_s1 * 1e3, "GB/s": nbytes / (ms_full * 1e-3) / 1e9,
+            "stage1_frac": nbytes / (ms_s1 * 1e-3) / 1e9 / peak, "us_per_layer_generic_kernel": ms_generic * 1e3}
 
 
 def triton_reference_leg(spec, dev, op, args):

@@ -44,7 +44,12 @@ typedef enum WsvdDtype { WSVD_I8 = 0, WSVD_F16 = 1, WSVD_F32 = 2 /* quant-append
 typedef enum WsvdRopeLayout { WSVD_ROPE_HALF = 0, WSVD_ROPE_INTERLEAVED = 1 } WsvdRopeLayout;
 
 /* Which stage-1 kernel to run.  AUTO picks the tcgen05 kernel when the shape allows. */
-typedef enum WsvdKernel { WSVD_KERNEL_AUTO = 0, WSVD_KERNEL_GENERIC = 1, WSVD_KERNEL_TC = 2 } WsvdKernel;
+typedef enum WsvdKernel {
+  WSVD_KERNEL_AUTO = 0,     /* tcgen05 kernel if the problem fits it, else warp-MMA, else generic */
+  WSVD_KERNEL_GENERIC = 1,  /* CUDA-core kernel, any shape */
+  WSVD_KERNEL_TC = 2,       /* tcgen05 + TMA kernel or WSVD_ERR_UNSUPPORTED */
+  WSVD_KERNEL_MMA = 3       /* warp-MMA kernel (f16 or int8 latents, head_dim 16..128, even ranks) or WSVD_ERR_UNSUPPORTED */
+} WsvdKernel;
 
 /*
  * Arguments of the latent decode-attention op.  Mirrors the tensors that

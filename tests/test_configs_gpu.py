@@ -220,7 +220,7 @@ def test_unknown_token_slot_count_takes_the_gather_path():
     assert_close(out, oracle_for(case, wv=True), "n_token_slots=0")
 
 
-@pytest.mark.parametrize("kernel", ["generic", "tc"])
+@pytest.mark.parametrize("kernel", ["generic", "tc", "mma"])
 def test_position_offsets(kernel):
     """pos_offset[b] shifts the RoPE position of every token of sequence b."""
     lens = [300, 1, 513]

@@ -11,7 +11,7 @@ from wsvd_b200.kernel.flash_decoding import (
 
 pytestmark = pytest.mark.gpu
 
-KERNELS = ["generic", "tc"]
+KERNELS = ["generic", "tc", "mma"]
 
 
 def run_i8(case, kernel, wv=False, **kw):
@@ -98,9 +98,9 @@ def test_long_positions_against_fp64(kernel):
     assert_close(got, oracle_for(case, wv=True, dtype=torch.float64), "32k vs fp64")
 
 
-@pytest.mark.parametrize("kernel", ["generic"])
+@pytest.mark.parametrize("kernel", ["generic", "mma"])
 @pytest.mark.parametrize("d,rk,rv", [(16, 16, 16), (32, 16, 32), (64, 32, 48)])
-def test_small_head_dims_generic(kernel, d, rk, rv):
+def test_small_head_dims(kernel, d, rk, rv):
     case = inputs.make_case(2, 2, d, rk, rv, [100, 37], 100, seed=d)
     assert_close(run_i8(case, kernel), oracle_for(case), f"D={d}")
 

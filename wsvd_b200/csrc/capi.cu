@@ -34,17 +34,18 @@ int validate(const WsvdLatentDecodeParams* p, bool need_out) {
   if (p->rank_k <= 0 || p->rank_k > 128 || p->rank_v <= 0 || p->rank_v > 128) return WSVD_ERR_BAD_SHAPE;
   if (p->batch > 65535 || p->n_q_heads > 65535) return WSVD_ERR_TOO_LARGE;
   if (p->split_len < 0) return WSVD_ERR_BAD_SHAPE;
-  if (p->kernel < WSVD_KERNEL_AUTO || p->kernel > WSVD_KERNEL_TC) return WSVD_ERR_BAD_DTYPE;
+  if (p->kernel < WSVD_KERNEL_AUTO || p->kernel > WSVD_KERNEL_MMA) return WSVD_ERR_BAD_DTYPE;
   if (!(p->theta > 0.f)) return WSVD_ERR_BAD_SHAPE;
   return WSVD_OK;
 }
 
 bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; }
 
-// The tensor-core kernel covers the decode shapes of the 7B/13B models; everything else
-// runs on the generic kernel.
+// The tcgen05 kernel covers the decode shapes of the 7B/13B models with an int8 cache; the
+// warp-MMA kernel takes f16 latents, other head dimensions and any even rank; the rest runs on the
+// generic kernel.
 bool tc_eligible(const WsvdLatentDecodeParams* p) {
-  if (p->kernel == WSVD_KERNEL_GENERIC) return false;
+  if (p->kernel == WSVD_KERNEL_GENERIC || p->kernel == WSVD_KERNEL_MMA) return false;
   if (p->head_dim != 128) return false;
   if (p->rank_k % 16 != 0 || p->rank_k > 64 || p->rank_v % 16 != 0 || p->rank_v > 64) return false;
   if (p->latent_dtype != WSVD_I8) return false;
@@ -56,6 +57,27 @@ bool tc_eligible(const WsvdLatentDecodeParams* p) {
   if (p->k_stride_t % 16 || p->k_stride_h % 16 || p->v_stride_t % 16 || p->v_stride_h % 16) return false;
   if (p->rope_table && (!aligned16(p->rope_table) || p->rope_table_rows < ((p->max_len + 127) / 128) * 128))
     return false;
+  return true;
+}
+
+// the caller's position table serves the warp-MMA kernel too ([2][rows][64] f16 is its layout for head_dim 128)
+bool mma_caller_table(const WsvdLatentDecodeParams* p) {
+  return p->rope_table && p->head_dim == 128 && aligned16(p->rope_table) &&
+         p->rope_table_rows >= ((p->max_len + 127) / 128) * 128;
+}
+
+bool mma_eligible(const WsvdLatentDecodeParams* p) {
+  if (p->kernel == WSVD_KERNEL_GENERIC || p->kernel == WSVD_KERNEL_TC) return false;
+  if (p->head_dim < 16) return false;
+  // pairs of latents are loaded at once
+  if (p->rank_k % 2 || p->rank_v % 2) return false;
+  if (p->k_stride_t % 2 || p->k_stride_h % 2 || p->v_stride_t % 2 || p->v_stride_h % 2) return false;
+  // token strides are multiplied as 32-bit values
+  if (p->k_stride_t < 0 || p->k_stride_t > INT32_MAX || p->v_stride_t < 0 || p->v_stride_t > INT32_MAX) return false;
+  const uintptr_t pair = p->latent_dtype == WSVD_I8 ? 1 : 3;
+  if ((reinterpret_cast<uintptr_t>(p->latent_k) & pair) || (reinterpret_cast<uintptr_t>(p->latent_v) & pair)) return false;
+  // with position offsets the table must reach max(pos_offset) + max_len, which only the caller knows
+  if (p->pos_offset != nullptr && !mma_caller_table(p)) return false;
   return true;
 }
 
@@ -76,6 +98,17 @@ void plan(const WsvdLatentDecodeParams* p, int* split_len, int* n_splits) {
     len = ((len + 127) / 128) * 128;
     if (len < 128) len = 128;
     if (len > 8192) len = 8192;
+    sl = (int)len;
+  } else if (sl <= 0 && mma_eligible(p)) {
+    // one CTA per (split, group of 4 heads, sequence), three resident per SM: a few waves of them
+    const long items = (long)p->batch * ((p->n_q_heads + 3) / 4);
+    const long target = 148L * 8;
+    long want = items > 0 ? (target + items - 1) / items : 1;
+    if (want < 1) want = 1;
+    long len = (p->max_len + want - 1) / want;
+    len = ((len + 127) / 128) * 128;
+    if (len < 256) len = 256;
+    if (len > 4096) len = 4096;
     sl = (int)len;
   } else if (sl <= 0) {
     // enough (b, h, split) items to fill 148 SMs a few times over, but never splits
@@ -116,6 +149,19 @@ int run_stage1(const wsvd::KArgs& a, void* scratch_table, const wsvd::Stage1Work
   const bool tc = tc_eligible(&a.p) && a.split_len % 128 == 0 && (a.p.rope_table || scratch_table);
   if (!tc) {
     if (a.p.kernel == WSVD_KERNEL_TC) return WSVD_ERR_UNSUPPORTED;
+    if (mma_eligible(&a.p) && (mma_caller_table(&a.p) || scratch_table)) {
+      const void* table = a.p.rope_table;
+      int rows = a.p.rope_table_rows;
+      if (!mma_caller_table(&a.p)) {
+        rows = table_rows_for(a.p.max_len);
+        cudaError_t e = wsvd::launch_mma_table(scratch_table, rows, a, stream);
+        if (e != cudaSuccess) return cuda_fail(e);
+        table = scratch_table;
+      }
+      cudaError_t e = wsvd::launch_stage1_mma(a, table, rows, stream);
+      return e == cudaSuccess ? WSVD_OK : cuda_fail(e);
+    }
+    if (a.p.kernel == WSVD_KERNEL_MMA) return WSVD_ERR_UNSUPPORTED;
     cudaError_t e = wsvd::launch_stage1_generic(a, stream);
     return e == cudaSuccess ? WSVD_OK : cuda_fail(e);
   }
@@ -145,6 +191,7 @@ struct Layout {
   size_t prefix_off;    // balanced mode only
   size_t arrivals_off;  // balanced mode only
   size_t table_off;
+  size_t table_bytes;   // 0: the caller's table is used, or the kernel needs none
   size_t total;
 };
 Layout workspace_layout(const WsvdLatentDecodeParams* p, int n_splits) {
@@ -161,8 +208,12 @@ Layout workspace_layout(const WsvdLatentDecodeParams* p, int n_splits) {
     off += align256((size_t)p->batch * p->n_q_heads * sizeof(uint32_t));
   }
   l.table_off = off;
-  if (tc_eligible(p) && !p->rope_table) off += wsvd::rope_table_bytes(table_rows_for(p->max_len));
-  l.total = off;
+  if (tc_eligible(p)) {
+    if (!p->rope_table) l.table_bytes = wsvd::rope_table_bytes(table_rows_for(p->max_len));
+  } else if (mma_eligible(p) && !mma_caller_table(p)) {
+    l.table_bytes = wsvd::mma_table_bytes(table_rows_for(p->max_len), p->head_dim);
+  }
+  l.total = off + l.table_bytes;
   return l;
 }
 
@@ -304,7 +355,7 @@ static int decode_impl(const WsvdLatentDecodeParams* p, const WsvdPeerSet* peers
   wsvd::KArgs a;
   fill_args(p, mid_o, lse, sl, ns, &a);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  void* scratch_table = p->rope_table ? nullptr : ws + l.table_off;
+  void* scratch_table = l.table_bytes ? ws + l.table_off : nullptr;
   wsvd::PartialIndex where = {nullptr, 0, ns, sl};
   wsvd::Stage1Work work = {0, nullptr, nullptr, nullptr};
   wsvd::PeerArgs pa;

@@ -166,6 +166,10 @@ struct Stage1Work {
 cudaError_t launch_stage1_tc(const KArgs& a, const void* table, int table_rows, const Stage1Work& work,
                              cudaStream_t stream);
 cudaError_t launch_rope_table(void* table, int rows, const KArgs& a, cudaStream_t stream);
+// warp-MMA kernel: its table is [2][rows][head_dim / 2] f16 (the same bytes as the table above for head_dim 128)
+cudaError_t launch_stage1_mma(const KArgs& a, const void* table, int rows, cudaStream_t stream);
+cudaError_t launch_mma_table(void* table, int rows, const KArgs& a, cudaStream_t stream);
+size_t mma_table_bytes(int rows, int head_dim);
 size_t rope_table_bytes(int rows);
 cudaError_t read_tc_status(unsigned int* out);
 cudaError_t reset_tc_status();

@@ -16,7 +16,7 @@ from ._lib import LatentDecodeParams, check
 
 I8, F16 = 0, 1
 ROPE = {"half": 0, "interleaved": 1}
-KERNEL = {"auto": 0, "generic": 1, "tc": 2}
+KERNEL = {"auto": 0, "generic": 1, "tc": 2, "mma": 3}
 
 
 def _ptr(t: Optional[torch.Tensor]):
