@@ -63,6 +63,9 @@ __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
+__device__ __forceinline__ void prefetch_l2(const void* ptr) {
+  asm volatile("prefetch.global.L2 [%0];\n" ::"l"(ptr));
+}
 // barrier among the four warps of one tile parity
 __device__ __forceinline__ void group_sync(int parity) {
   asm volatile("bar.sync %0, %1;\n" ::"r"(1 + parity), "r"(kHeads * 32) : "memory");
@@ -215,11 +218,15 @@ stage1_mma_kernel(const __grid_constant__ KArgs a, const __half* __restrict__ ta
   request_table_tile(lo + parity * 16, 0);
   __syncthreads();  // [P; Q] complete
 
-  // token slots of this thread's two rows, fetched one tile ahead (rows past the end take the last valid token)
-  int t0_next = 0, t1_next = 0;
+  // token slots of this thread's two rows, fetched two tiles ahead (rows past the end take the last
+  // valid token): a tile's slots are in registers when the tile before it starts, which then asks
+  // for the tile's K and V rows to be brought into L2
+  int t0_next = 0, t1_next = 0, t0_after = 0, t1_after = 0;
   if (live && lo + parity * 16 < hi) {
     t0_next = page[min(lo + parity * 16 + g, hi - 1)];
     t1_next = page[min(lo + parity * 16 + g + 8, hi - 1)];
+    t0_after = page[min(lo + parity * 16 + g + 32, hi - 1)];
+    t1_after = page[min(lo + parity * 16 + g + 40, hi - 1)];
   }
 
   int it = 0;
@@ -228,9 +235,18 @@ stage1_mma_kernel(const __grid_constant__ KArgs a, const __half* __restrict__ ta
     const int s0 = s_base + g, s1 = s0 + 8;
     const bool ok0 = s0 < hi, ok1 = s1 < hi;
     const int t0 = t0_next, t1 = t1_next;
+    t0_next = t0_after;
+    t1_next = t1_after;
     if (live && s_base + 32 < hi) {
-      t0_next = page[min(s0 + 32, hi - 1)];
-      t1_next = page[min(s1 + 32, hi - 1)];
+      // the next tile's rows toward L2: lanes 0-15 take a K row each, lanes 16-31 a V row
+      const int row = lane & 15;
+      const int tt = __shfl_sync(0xffffffffu, row < 8 ? t0_next : t1_next, (row & 7) * 4);
+      const char* ptr = lane < 16 ? reinterpret_cast<const char*>(lk_base + (int64_t)tt * k_st)
+                                  : reinterpret_cast<const char*>(lv_base + (int64_t)tt * v_st);
+      prefetch_l2(ptr);
+      if ((lane < 16 ? Rk : Rv) * (int)sizeof(LT) > 128) prefetch_l2(ptr + 128);
+      t0_after = page[min(s0 + 64, hi - 1)];
+      t1_after = page[min(s1 + 64, hi - 1)];
     }
     uint32_t kw0[kWords], kw1[kWords];
     uint32_t vw[16], vx[16];  // the tile's 16 V rows: this lane's pair of ranks (and the pair 64 further)
