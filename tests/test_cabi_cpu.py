@@ -105,6 +105,30 @@ def test_split_plan_is_consistent_with_workspace_size():
             assert need >= p.batch * p.n_q_heads * ns.value * (p.rank_v + 1) * 4
 
 
+def test_warp_mma_kernel_plan_and_workspace():
+    """f16 latents, rank 62, head_dim 64: shapes of the warp-MMA kernel.  Its plan cuts the context into
+    fixed splits of 256..4096 tokens, and the workspace holds the partials plus a position table of
+    [2][rows][head_dim / 2] f16 when the caller passes none."""
+    lib = _lib.lib()
+    for head_dim, rk, rv, dtype in [(128, 64, 64, 1), (128, 62, 62, 0), (64, 40, 24, 1), (128, 128, 96, 1)]:
+        for kernel in (0, 3):
+            p = _params(head_dim=head_dim, rank_k=rk, rank_v=rv, latent_dtype=dtype, kernel=kernel, max_len=8192,
+                        k_scale=0x1000 if dtype == 0 else None, v_scale=0x1000 if dtype == 0 else None,
+                        k_stride_t=rk, k_stride_h=8192 * rk, v_stride_t=rv, v_stride_h=8192 * rv)
+            sl, ns = ctypes.c_int32(), ctypes.c_int32()
+            assert lib.wsvd_latent_decode_plan(ctypes.byref(p), ctypes.byref(sl), ctypes.byref(ns)) == 0
+            assert 256 <= sl.value <= 4096 and sl.value % 128 == 0 and ns.value * sl.value >= 8192
+            need = lib.wsvd_latent_decode_workspace_bytes(ctypes.byref(p))
+            partials = p.batch * p.n_q_heads * ns.value * (rv + 1) * 4
+            assert need >= partials + 8192 * head_dim * 2
+    # an odd rank is not a shape of this kernel: no table in the workspace, the generic kernel's plan
+    p = _params(rank_k=63, latent_dtype=1, k_scale=None, v_scale=None, max_len=8192)
+    sl, ns = ctypes.c_int32(), ctypes.c_int32()
+    assert lib.wsvd_latent_decode_plan(ctypes.byref(p), ctypes.byref(sl), ctypes.byref(ns)) == 0
+    need = lib.wsvd_latent_decode_workspace_bytes(ctypes.byref(p))
+    assert need < p.batch * p.n_q_heads * ns.value * (p.rank_v + 1) * 4 + 4096
+
+
 def test_empty_batch_is_a_no_op():
     lib = _lib.lib()
     p = _params(batch=0)
