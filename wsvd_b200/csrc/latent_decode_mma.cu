@@ -138,27 +138,39 @@ stage1_mma_kernel(const __grid_constant__ KArgs a, const __half* __restrict__ ta
     }
     __half* rows = Bs + (size_t)hh * NT * 8 * ldb;
     const bool wk_i8 = p.wk_dtype == WSVD_I8;
-#pragma unroll 8
-    for (int nrow = r_first; nrow < NT * 8; nrow += r_step) {
-      const int r = kMine * ((nrow & 7) >> 1) + 2 * (nrow >> 3) + (nrow & 1);
-      float pv = 0.f, qv = 0.f;
-      if (on_head && r < Rk) {
-        const int64_t off = (int64_t)r * p.wk_stride_r + (int64_t)hkk * D;
-        float u0, u1;
-        if (wk_i8) {
-          const int8_t* w = reinterpret_cast<const int8_t*>(p.wk) + off;
-          u0 = (float)w[d0] * s0;
-          u1 = (float)w[d1] * s1;
-        } else {
-          const __half* w = reinterpret_cast<const __half*>(p.wk) + off;
-          u0 = __half2float(w[d0]);
-          u1 = __half2float(w[d1]);
+    const int64_t col = (int64_t)hkk * D;
+    auto rank_of = [](int nrow) { return kMine * ((nrow & 7) >> 1) + 2 * (nrow >> 3) + (nrow & 1); };
+    // Eight rows at a time: their loads of U are unconditional (row and rank clamped to valid ones),
+    // so all sixteen are in flight together instead of one L2 round trip per row.
+    constexpr int kBatch = 8;
+    for (int base = r_first; base < NT * 8; base += r_step * kBatch) {
+      float u0[kBatch], u1[kBatch];
+      if (wk_i8) {
+        const int8_t* w = reinterpret_cast<const int8_t*>(p.wk) + col;
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k) {
+          const int64_t off = (int64_t)min(rank_of(min(base + k * r_step, NT * 8 - 1)), Rk - 1) * p.wk_stride_r;
+          u0[k] = (float)w[off + d0] * s0;
+          u1[k] = (float)w[off + d1] * s1;
         }
-        pv = q0 * u0 + q1 * u1;
-        qv = q1 * u0 - q0 * u1;
+      } else {
+        const __half* w = reinterpret_cast<const __half*>(p.wk) + col;
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k) {
+          const int64_t off = (int64_t)min(rank_of(min(base + k * r_step, NT * 8 - 1)), Rk - 1) * p.wk_stride_r;
+          u0[k] = __half2float(w[off + d0]);
+          u1[k] = __half2float(w[off + d1]);
+        }
       }
-      rows[nrow * ldb + i] = __float2half_rn(pv);
-      rows[nrow * ldb + h2 + i] = __float2half_rn(qv);
+#pragma unroll
+      for (int k = 0; k < kBatch; ++k) {
+        const int nrow = base + k * r_step;
+        if (nrow < NT * 8) {
+          const bool on = on_head && rank_of(nrow) < Rk;
+          rows[nrow * ldb + i] = __float2half_rn(on ? q0 * u0[k] + q1 * u1[k] : 0.f);
+          rows[nrow * ldb + h2 + i] = __float2half_rn(on ? q1 * u0[k] - q0 * u1[k] : 0.f);
+        }
+      }
     }
   }
 
