@@ -22,7 +22,7 @@
 // read it as the A operand with ldmatrix.  W stays in the accumulators, where the thread that
 // holds W[s, r] multiplies it with Lk[s, r]; the ranks are assigned to accumulator columns so
 // that a thread's share of a K row is one contiguous run, fetched with 16-byte loads.  A tile's K
-// and V rows are requested before its MMAs and consumed after them.
+// and V rows are requested a tile ahead, as soon as the registers that receive them are free.
 #include "common.cuh"
 
 namespace wsvd {
@@ -63,9 +63,6 @@ __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
-__device__ __forceinline__ void prefetch_l2(const void* ptr) {
-  asm volatile("prefetch.global.L2 [%0];\n" ::"l"(ptr));
-}
 // barrier among the four warps of one tile parity
 __device__ __forceinline__ void group_sync(int parity) {
   asm volatile("bar.sync %0, %1;\n" ::"r"(1 + parity), "r"(kHeads * 32) : "memory");
@@ -230,15 +227,75 @@ stage1_mma_kernel(const __grid_constant__ KArgs a, const __half* __restrict__ ta
   request_table_tile(lo + parity * 16, 0);
   __syncthreads();  // [P; Q] complete
 
+  // A tile's K rows (with their scales) and V rows live in registers from the moment the tile before
+  // it has consumed its own: K is requested right after the previous tile's scores, V right after its
+  // P.V, so their latency runs under the rest of that tile and the MMAs of this one.
+  uint32_t kw0[kWords], kw1[kWords];
+  uint32_t vw[16], vx[16];  // the tile's 16 V rows: this lane's pair of ranks (and the pair 64 further)
+  float sk0 = 1.f, sk1 = 1.f, sv0 = 1.f, sv1 = 1.f;
+  auto load_k = [&](int ta, int tb) {
+    const LT* lk0 = lk_base + (int64_t)ta * k_st + rk_first;
+    const LT* lk1 = lk_base + (int64_t)tb * k_st + rk_first;
+    if (k_all) {
+#pragma unroll
+      for (int v = 0; v < kWords / 4; ++v) {
+        *reinterpret_cast<uint4*>(&kw0[4 * v]) = __ldg(reinterpret_cast<const uint4*>(lk0) + v);
+        *reinterpret_cast<uint4*>(&kw1[4 * v]) = __ldg(reinterpret_cast<const uint4*>(lk1) + v);
+      }
+    } else if (sizeof(LT) == 2) {
+#pragma unroll
+      for (int e = 0; e < kWords; ++e) {
+        const bool on = rk_first + 2 * e < Rk;  // rank_k is even: a pair never straddles the end
+        kw0[e] = on ? *reinterpret_cast<const uint32_t*>(lk0 + 2 * e) : 0u;
+        kw1[e] = on ? *reinterpret_cast<const uint32_t*>(lk1 + 2 * e) : 0u;
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < kWords; ++e) {
+        const bool on_a = rk_first + 4 * e < Rk, on_b = rk_first + 4 * e + 2 < Rk;
+        const uint32_t a0 = on_a ? *reinterpret_cast<const uint16_t*>(lk0 + 4 * e) : 0u;
+        const uint32_t b0 = on_b ? *reinterpret_cast<const uint16_t*>(lk0 + 4 * e + 2) : 0u;
+        const uint32_t a1 = on_a ? *reinterpret_cast<const uint16_t*>(lk1 + 4 * e) : 0u;
+        const uint32_t b1 = on_b ? *reinterpret_cast<const uint16_t*>(lk1 + 4 * e + 2) : 0u;
+        kw0[e] = a0 | (b0 << 16);
+        kw1[e] = a1 | (b1 << 16);
+      }
+    }
+    if (ks_base) {
+      sk0 = __half2float(ks_base[(int64_t)ta * p.ks_stride_t + (int64_t)hk * p.ks_stride_h]);
+      sk1 = __half2float(ks_base[(int64_t)tb * p.ks_stride_t + (int64_t)hk * p.ks_stride_h]);
+    }
+  };
+  auto load_v = [&](int ta, int tb) {
+    if (vs_base) {
+      sv0 = __half2float(vs_base[(int64_t)ta * p.vs_stride_t + (int64_t)hk * p.vs_stride_h]);
+      sv1 = __half2float(vs_base[(int64_t)tb * p.vs_stride_t + (int64_t)hk * p.vs_stride_h]);
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int tt = __shfl_sync(0xffffffffu, i < 8 ? ta : tb, (i & 7) * 4);
+      const LT* lv = lv_base + (int64_t)tt * v_st;
+      vx[i] = 0u;
+      if (sizeof(LT) == 2) {
+        vw[i] = rv0 < Rv ? *reinterpret_cast<const uint32_t*>(lv + rv0) : 0u;
+        if (wide_v) vx[i] = rv1 < Rv ? *reinterpret_cast<const uint32_t*>(lv + rv1) : 0u;
+      } else {
+        vw[i] = rv0 < Rv ? *reinterpret_cast<const uint16_t*>(lv + rv0) : 0u;
+        if (wide_v) vx[i] = rv1 < Rv ? *reinterpret_cast<const uint16_t*>(lv + rv1) : 0u;
+      }
+    }
+  };
+
   // token slots of this thread's two rows, fetched two tiles ahead (rows past the end take the last
-  // valid token): a tile's slots are in registers when the tile before it starts, which then asks
-  // for the tile's K and V rows to be brought into L2
+  // valid token): the slots of the next tile are in registers when this tile asks for its K and V
   int t0_next = 0, t1_next = 0, t0_after = 0, t1_after = 0;
   if (live && lo + parity * 16 < hi) {
     t0_next = page[min(lo + parity * 16 + g, hi - 1)];
     t1_next = page[min(lo + parity * 16 + g + 8, hi - 1)];
     t0_after = page[min(lo + parity * 16 + g + 32, hi - 1)];
     t1_after = page[min(lo + parity * 16 + g + 40, hi - 1)];
+    load_k(t0_next, t1_next);
+    load_v(t0_next, t1_next);
   }
 
   int it = 0;
@@ -246,78 +303,19 @@ stage1_mma_kernel(const __grid_constant__ KArgs a, const __half* __restrict__ ta
     // this thread's two rows of the tile; rows past the end count as -inf
     const int s0 = s_base + g, s1 = s0 + 8;
     const bool ok0 = s0 < hi, ok1 = s1 < hi;
-    const int t0 = t0_next, t1 = t1_next;
-    t0_next = t0_after;
+    const bool more = s_base + 32 < hi;  // this warp has another tile after this one
+    t0_next = t0_after;                  // now the next tile's slots
     t1_next = t1_after;
-    if (live && s_base + 32 < hi) {
-      // the next tile's rows toward L2: lanes 0-15 take a K row each, lanes 16-31 a V row
-      const int row = lane & 15;
-      const int tt = __shfl_sync(0xffffffffu, row < 8 ? t0_next : t1_next, (row & 7) * 4);
-      const char* ptr = lane < 16 ? reinterpret_cast<const char*>(lk_base + (int64_t)tt * k_st)
-                                  : reinterpret_cast<const char*>(lv_base + (int64_t)tt * v_st);
-      prefetch_l2(ptr);
-      if ((lane < 16 ? Rk : Rv) * (int)sizeof(LT) > 128) prefetch_l2(ptr + 128);
+    if (live && more) {
       t0_after = page[min(s0 + 64, hi - 1)];
       t1_after = page[min(s1 + 64, hi - 1)];
-    }
-    uint32_t kw0[kWords], kw1[kWords];
-    uint32_t vw[16], vx[16];  // the tile's 16 V rows: this lane's pair of ranks (and the pair 64 further)
-    float sk0 = 1.f, sk1 = 1.f, sv0 = 1.f, sv1 = 1.f;
-    if (live) {
-      const LT* lk0 = lk_base + (int64_t)t0 * k_st + rk_first;
-      const LT* lk1 = lk_base + (int64_t)t1 * k_st + rk_first;
-      if (k_all) {
-#pragma unroll
-        for (int v = 0; v < kWords / 4; ++v) {
-          *reinterpret_cast<uint4*>(&kw0[4 * v]) = __ldg(reinterpret_cast<const uint4*>(lk0) + v);
-          *reinterpret_cast<uint4*>(&kw1[4 * v]) = __ldg(reinterpret_cast<const uint4*>(lk1) + v);
-        }
-      } else if (sizeof(LT) == 2) {
-#pragma unroll
-        for (int e = 0; e < kWords; ++e) {
-          const bool on = rk_first + 2 * e < Rk;  // rank_k is even: a pair never straddles the end
-          kw0[e] = on ? *reinterpret_cast<const uint32_t*>(lk0 + 2 * e) : 0u;
-          kw1[e] = on ? *reinterpret_cast<const uint32_t*>(lk1 + 2 * e) : 0u;
-        }
-      } else {
-#pragma unroll
-        for (int e = 0; e < kWords; ++e) {
-          const bool on_a = rk_first + 4 * e < Rk, on_b = rk_first + 4 * e + 2 < Rk;
-          const uint32_t a0 = on_a ? *reinterpret_cast<const uint16_t*>(lk0 + 4 * e) : 0u;
-          const uint32_t b0 = on_b ? *reinterpret_cast<const uint16_t*>(lk0 + 4 * e + 2) : 0u;
-          const uint32_t a1 = on_a ? *reinterpret_cast<const uint16_t*>(lk1 + 4 * e) : 0u;
-          const uint32_t b1 = on_b ? *reinterpret_cast<const uint16_t*>(lk1 + 4 * e + 2) : 0u;
-          kw0[e] = a0 | (b0 << 16);
-          kw1[e] = a1 | (b1 << 16);
-        }
-      }
-      if (ks_base) {
-        sk0 = __half2float(ks_base[(int64_t)t0 * p.ks_stride_t + (int64_t)hk * p.ks_stride_h]);
-        sk1 = __half2float(ks_base[(int64_t)t1 * p.ks_stride_t + (int64_t)hk * p.ks_stride_h]);
-        sv0 = __half2float(vs_base[(int64_t)t0 * p.vs_stride_t + (int64_t)hk * p.vs_stride_h]);
-        sv1 = __half2float(vs_base[(int64_t)t1 * p.vs_stride_t + (int64_t)hk * p.vs_stride_h]);
-      }
-      // V rows of the tile, requested before the MMAs and used after the softmax
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const int tt = __shfl_sync(0xffffffffu, i < 8 ? t0 : t1, (i & 7) * 4);
-        const LT* lv = lv_base + (int64_t)tt * v_st;
-        vx[i] = 0u;
-        if (sizeof(LT) == 2) {
-          vw[i] = rv0 < Rv ? *reinterpret_cast<const uint32_t*>(lv + rv0) : 0u;
-          if (wide_v) vx[i] = rv1 < Rv ? *reinterpret_cast<const uint32_t*>(lv + rv1) : 0u;
-        } else {
-          vw[i] = rv0 < Rv ? *reinterpret_cast<const uint16_t*>(lv + rv0) : 0u;
-          if (wide_v) vx[i] = rv1 < Rv ? *reinterpret_cast<const uint16_t*>(lv + rv1) : 0u;
-        }
-      }
     }
 
     // the tile's table rows have landed (own copies, then everybody's); every warp of the group is
     // also past the previous tile, so its buffer can take the next one
     cp_async_wait_all();
     group_sync(parity);
-    if (s_base + 32 < hi) request_table_tile(s_base + 32, (it + 1) & 1);
+    if (more) request_table_tile(s_base + 32, (it + 1) & 1);
     if (!live) continue;
 
     // W tile: 16 tokens x NT*8 ranks
@@ -354,6 +352,7 @@ stage1_mma_kernel(const __grid_constant__ KArgs a, const __half* __restrict__ ta
     z1 += __shfl_xor_sync(0xffffffffu, z1, 2);
     z0 = ok0 ? z0 * sk0 : -INFINITY;
     z1 = ok1 ? z1 * sk1 : -INFINITY;
+    if (more) load_k(t0_next, t1_next);  // this tile's K is consumed
 
     // online softmax over the tile (row s_base is always valid, so the maximum is finite)
     float tmax = fmaxf(z0, z1);
@@ -386,6 +385,7 @@ stage1_mma_kernel(const __grid_constant__ KArgs a, const __half* __restrict__ ta
         acc[3] = fmaf(pw, vb.y, acc[3]);
       }
     }
+    if (more) load_v(t0_next, t1_next);  // this tile's V is consumed
   }
 
   cp_async_wait_all();  // a group without tiles still has its first request in flight
